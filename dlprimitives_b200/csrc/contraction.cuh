@@ -1,0 +1,124 @@
+// One description for every dense contraction on the hot path.
+//
+// Convolution (implicit GEMM, src/core/conv.cpp:59-80 in the reference), 1x1 convolution, InnerProduct
+// and the plain GEMM interface are all   D[row, col] = sum_k  A(row, k) * B(col, k)   with
+//   row = an output pixel (batch, oy, ox)  or a row of the GEMM's C,
+//   col = an output channel               or a column of C,
+//   k   = (input channel, ky, kx)         or the GEMM's K.
+// The A side is read straight from the caller's tensor (NCHW activations or a row-major /
+// transposed matrix), never re-laid-out in memory; the B side (weights) is either raw or pre-packed.
+#pragma once
+#include "common.cuh"
+
+namespace dlp {
+
+enum : int {
+    A_GATHER = 0,  // general convolution: address = row_base + ktab[k].offset, bounds-checked per tap
+    A_STRIDED = 1  // address = row_base + k * a_k_stride (1x1 stride-1 convolution, matrices)
+};
+enum : int {
+    OUT_NCHW = 0,     // row = (b, pix): y[(b * out_channels_total + col) * out_plane + pix]
+    OUT_ROW_MAJOR = 1 // y[row * ldc + col]
+};
+
+struct KTap {
+    int offset;  // element offset of tap k from the row's base address: c*H*W + dy*W + dx
+    int dydx;    // (dy << 16) | dx, the tap's displacement for the bounds check; 0x7fff7fff marks padding
+};
+
+struct Contraction {
+    // sizes
+    long long rows;      // M: batch*OH*OW or GEMM M
+    int cols;            // N: output channels of this group or GEMM N
+    int k;               // true K
+    // A side
+    const float *a;
+    int a_mode;          // A_GATHER / A_STRIDED
+    long long a_k_stride;
+    long long a_row_stride;   // A_STRIDED matrices: base = row * a_row_stride (used when plane == 0)
+    // convolution geometry (A_GATHER and A_STRIDED with plane > 0)
+    int plane;           // OH*OW (0 = matrix addressing)
+    int out_w;
+    int in_h, in_w;
+    int stride_h, stride_w, pad_h, pad_w;
+    long long a_batch_stride;  // Cin_total*H*W
+    const KTap *ktab;    // k_pad entries
+    // B side, raw form: B(col, k) = b[col * b_col_stride + k * b_k_stride]
+    const float *b;
+    long long b_col_stride, b_k_stride;
+    // output
+    float *y;
+    int out_mode;
+    long long ldc;            // OUT_ROW_MAJOR
+    int out_channels_total;   // OUT_NCHW: channels of the whole output tensor
+    const float *bias;
+    int bias_mode;            // DLP_GEMM_NO_BIAS / BIAS_M (per row) / BIAS_N (per col)
+    int act;
+    float beta;               // y = beta*y_old + act(...)
+    const float *residual;    // optional, same addressing as y
+    float residual_scale;
+    int post_act;
+};
+
+// Row (pixel) coordinates shared by the loaders.
+struct RowInfo {
+    long long base;  // element offset of the row's first tap (may be "negative" through padding)
+    int iy0, ix0;    // input coordinates of tap (0,0)
+    long long out;   // element offset of the row in y (without the column term)
+    bool valid;
+};
+
+__device__ __forceinline__ RowInfo make_row(const Contraction &p, long long row)
+{
+    RowInfo r;
+    r.valid = row < p.rows;
+    if(!r.valid) row = 0;
+    if(p.plane > 0) {
+        int b = int(row / p.plane);
+        int pix = int(row - (long long)b * p.plane);
+        int oy = pix / p.out_w;
+        int ox = pix - oy * p.out_w;
+        r.iy0 = oy * p.stride_h - p.pad_h;
+        r.ix0 = ox * p.stride_w - p.pad_w;
+        r.base = (long long)b * p.a_batch_stride + (long long)r.iy0 * p.in_w + r.ix0;
+        r.out = p.out_mode == OUT_NCHW ? (long long)b * p.out_channels_total * p.plane + pix : row * p.ldc;
+    }
+    else {
+        r.iy0 = r.ix0 = 0;
+        r.base = row * p.a_row_stride;
+        r.out = row * p.ldc;
+    }
+    return r;
+}
+
+__device__ __forceinline__ long long out_index(const Contraction &p, const RowInfo &r, int col)
+{
+    return p.out_mode == OUT_NCHW ? r.out + (long long)col * p.plane : r.out + col;
+}
+
+__device__ __forceinline__ float finish_output(const Contraction &p, const RowInfo &r, long long row, int col, float acc)
+{
+    if(p.bias_mode == DLP_GEMM_BIAS_N) acc += __ldg(p.bias + col);
+    else if(p.bias_mode == DLP_GEMM_BIAS_M) acc += __ldg(p.bias + row);
+    acc = apply_act(acc, p.act);
+    long long idx = out_index(p, r, col);
+    if(p.residual) acc = apply_act(acc + p.residual_scale * __ldg(p.residual + idx), p.post_act);
+    if(p.beta != 0.0f) acc += p.beta * p.y[idx];
+    return acc;
+}
+
+// launchers (one per translation unit)
+dlp_status launch_contraction_ffma(const Contraction &p, int groups, long long a_group_stride, long long b_group_stride,
+                                   int out_group_channels, cudaStream_t stream);
+
+struct TcPacked {   // pre-packed B for the tensor-core kernel: [2][n_pad][k_pad] fp32 (hi plane, lo plane)
+    int bn;         // column tile: 64 or 128
+    int n_pad, k_pad;
+    size_t bytes() const { return size_t(2) * n_pad * k_pad * sizeof(float); }
+};
+TcPacked tc_packed_layout(int cols, int k);
+dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
+                      float *packed, cudaStream_t stream);
+dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream);
+
+} // namespace dlp

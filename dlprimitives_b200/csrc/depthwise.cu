@@ -1,0 +1,156 @@
+// Depthwise convolution forward (groups == channels, one filter per channel), stride 1 or 2.
+//
+// HBM-bound: about 2 flops per byte.  The job is to touch every input and output element once
+// with wide coalesced accesses.  In NCHW the planes of consecutive channels are contiguous, and so
+// is a band of full-width rows inside a plane, so a CTA's input is one contiguous run of floats: it
+// is copied to shared memory with 16-byte loads (whatever W is), the k x k taps are read from there,
+// and the outputs (again one contiguous run) are written with coalesced stores.
+//   small planes (7x7, 14x14 ...): several whole planes per CTA
+//   large planes (56x56, 112x112): one band of output rows of one plane per CTA
+// Bias, activation and y = factor*y_old + ... are fused.  The reference's counterpart is
+// src/kernels/depthwise_separable_conv.cl (stride 1 only; stride 2 goes to its grouped GEMM).
+#include "depthwise.cuh"
+
+namespace dlp {
+namespace {
+
+constexpr int THREADS = 256;
+constexpr int SMEM_FLOATS = 10240;   // 40 KB staging buffer
+
+struct DwParams {
+    const float *x, *w, *bias;
+    float *y;
+    int channels, H, W, OH, OW;
+    int stride, pad, ks;
+    int planes;            // batch * channels
+    int planes_per_cta;    // > 1 only when a band is the whole plane
+    int rows_per_band;     // output rows per CTA
+    int bands;             // bands per plane
+    int act;
+    float factor;
+};
+
+template<int KS>
+__global__ void __launch_bounds__(THREADS) depthwise_kernel(DwParams p)
+{
+    __shared__ __align__(16) float tile[SMEM_FLOATS];
+    const int ks = KS > 0 ? KS : p.ks;
+    const long long plane0 = (long long)(blockIdx.x / p.bands) * p.planes_per_cta;
+    const int band = blockIdx.x % p.bands;
+    const int np = int(min((long long)p.planes_per_cta, p.planes - plane0));
+    const int oy0 = band * p.rows_per_band;
+    const int oy1 = min(oy0 + p.rows_per_band, p.OH);
+    // input rows this band needs, clipped to the image
+    const int iy_lo = max(oy0 * p.stride - p.pad, 0);
+    const int iy_hi = min((oy1 - 1) * p.stride - p.pad + ks, p.H);
+    const int in_rows = iy_hi - iy_lo;
+    const long long plane_elems = (long long)p.H * p.W;
+    // contiguous run: np whole planes (bands == 1) or in_rows rows of one plane
+    const long long g_begin = plane0 * plane_elems + (long long)iy_lo * p.W;
+    const long long g_end = np > 1 ? (plane0 + np) * plane_elems : g_begin + (long long)in_rows * p.W;
+    const long long total_in = (long long)p.planes * plane_elems;
+    const long long a_begin = g_begin & ~3ll;                   // 16-byte aligned start (x is 16-byte aligned)
+    const int shift = int(g_begin - a_begin);
+    const int count = int(g_end - a_begin);
+
+    for(int i = threadIdx.x * 4; i < count; i += THREADS * 4) {
+        const long long gi = a_begin + i;
+        if(gi + 4 <= total_in) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(p.x + gi));
+            *reinterpret_cast<float4 *>(tile + i) = v;
+        }
+        else {
+            for(int j = 0; j < 4 && gi + j < total_in; j++) tile[i + j] = __ldg(p.x + gi + j);
+        }
+    }
+    __syncthreads();
+
+    const int out_rows = oy1 - oy0;
+    const int outs_per_plane = out_rows * p.OW;
+    const int total_out = np * outs_per_plane;
+    for(int o = threadIdx.x; o < total_out; o += THREADS) {
+        const int pl = o / outs_per_plane;
+        const int rem = o - pl * outs_per_plane;
+        const int oy = oy0 + rem / p.OW;
+        const int ox = rem % p.OW;
+        const long long plane = plane0 + pl;
+        const int c = int(plane % p.channels);
+        const float *wk = p.w + (long long)c * ks * ks;
+        // tile[t] holds global element a_begin + t; element (iy, ix) of this plane sits at src[iy*W + ix]
+        const float *src = tile + shift + (long long)pl * plane_elems - (long long)iy_lo * p.W;
+        const int iy0 = oy * p.stride - p.pad, ix0 = ox * p.stride - p.pad;
+        float acc = 0.0f;
+        #pragma unroll
+        for(int ky = 0; ky < (KS > 0 ? KS : 7); ky++) {
+            if(KS == 0 && ky >= ks) break;
+            const int iy = iy0 + ky;
+            if(unsigned(iy) >= unsigned(p.H)) continue;
+            #pragma unroll
+            for(int kx = 0; kx < (KS > 0 ? KS : 7); kx++) {
+                if(KS == 0 && kx >= ks) break;
+                const int ix = ix0 + kx;
+                if(unsigned(ix) >= unsigned(p.W)) continue;
+                acc = fmaf(src[iy * p.W + ix], __ldg(wk + ky * ks + kx), acc);
+            }
+        }
+        if(p.bias) acc += __ldg(p.bias + c);
+        acc = apply_act(acc, p.act);
+        const long long yi = plane * ((long long)p.OH * p.OW) + (long long)oy * p.OW + ox;
+        if(p.factor != 0.0f) acc += p.factor * p.y[yi];
+        p.y[yi] = acc;
+    }
+}
+
+} // namespace
+
+bool depthwise_supported(int ks_h, int ks_w, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int in_w)
+{
+    if(ks_h != ks_w || stride_h != stride_w || pad_h != pad_w || dil_h != 1 || dil_w != 1) return false;
+    if(ks_h < 1 || ks_h > 7 || stride_h < 1 || stride_h > 2) return false;
+    // one band must fit the staging buffer even at one output row
+    return (long long)(ks_h + 1) * in_w + 8 <= SMEM_FLOATS;
+}
+
+dlp_status launch_depthwise(const float *x, const float *w, const float *bias, float *y, int batch, int channels, int H, int W,
+                            int ks, int stride, int pad, int act, float factor, cudaStream_t stream)
+{
+    if(reinterpret_cast<uintptr_t>(x) % 16 != 0) return fail(DLP_INVALID_ARGUMENT, "depthwise input must be 16-byte aligned");
+    DwParams p;
+    p.x = x; p.w = w; p.bias = bias; p.y = y;
+    p.channels = channels; p.H = H; p.W = W;
+    p.OH = (H + 2 * pad - ks) / stride + 1;
+    p.OW = (W + 2 * pad - ks) / stride + 1;
+    p.stride = stride; p.pad = pad; p.ks = ks;
+    p.planes = batch * channels;
+    p.act = act; p.factor = factor;
+    if(p.planes <= 0 || p.OH <= 0 || p.OW <= 0) return DLP_OK;
+    const long long plane_elems = (long long)H * W;
+    const int budget = SMEM_FLOATS - 8;
+    if(plane_elems <= budget) {
+        p.bands = 1;
+        p.rows_per_band = p.OH;
+        int ppc = int(budget / plane_elems);
+        // keep at least ~4 CTAs per SM worth of blocks when the problem allows
+        const int want_blocks = 4 * sm_count();
+        ppc = std::max(1, std::min(ppc, int(ceil_div<long long>(p.planes, want_blocks))));
+        p.planes_per_cta = ppc;
+    }
+    else {
+        p.planes_per_cta = 1;
+        int rows = (budget / W - ks) / stride + 1;     // (rows-1)*stride + ks input rows fit
+        rows = std::max(1, std::min(rows, p.OH));
+        p.rows_per_band = rows;
+        p.bands = ceil_div(p.OH, rows);
+    }
+    const long long blocks = ceil_div<long long>(p.planes, p.planes_per_cta) * p.bands;
+    if(blocks > 0x7fffffffLL) return fail(DLP_INVALID_ARGUMENT, "depthwise problem too large for one launch");
+    switch(ks) {
+    case 3: depthwise_kernel<3><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
+    case 5: depthwise_kernel<5><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
+    default: depthwise_kernel<0><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
+    }
+    DLP_LAUNCH_OK("depthwise_kernel");
+    return DLP_OK;
+}
+
+} // namespace dlp
