@@ -24,6 +24,7 @@
 #include "contraction.cuh"
 #include <cuda.h>
 #include <mutex>
+#include <cstdlib>
 
 namespace dlp {
 
@@ -168,6 +169,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
                  : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ bool act_is_clamp(int act) { return act == DLP_ACT_IDENTITY || act == DLP_ACT_RELU || act == DLP_ACT_RELU6; }
+__device__ __forceinline__ float2 act_clamp(int act)
+{
+    return make_float2(act == DLP_ACT_IDENTITY ? -INFINITY : 0.0f, act == DLP_ACT_RELU6 ? 6.0f : INFINITY);
+}
+// Lean store of 32 accumulator columns of one row: y = clamp(acc + bias) [then clamp(y + s*residual)].
+template<bool BIAS, bool RES>
+__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], float *y0, const float *r0, long long cs, const float *b0,
+                                            float2 clamp, float res_scale, float2 post_clamp)
+{
+    #pragma unroll
+    for(int j = 0; j < 32; j++) {
+        float a = __uint_as_float(v[j]);
+        if(BIAS) a += __ldg(b0 + j);
+        a = fminf(fmaxf(a, clamp.x), clamp.y);
+        if(RES) {
+            a = a + res_scale * __ldg(r0 + j * cs);
+            a = fminf(fmaxf(a, post_clamp.x), post_clamp.y);
+        }
+        y0[j * cs] = a;
+    }
+}
+
 // Position of a loader in the CTA's sequence of k-blocks (the sequence runs on across tiles).
 struct Cursor {
     long long tile;
@@ -178,7 +202,7 @@ struct Cursor {
 template<int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contraction p, int n_pad, int kblocks, int n_tiles,
-                          long long num_tiles, int *status)
+                          long long num_tiles, int *status, int dbg)
 {
     extern __shared__ unsigned char smem_raw[];
     // B ring first, 1024-byte aligned as the 128B swizzle requires; barriers after it.
@@ -259,6 +283,7 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                     for(int j = 0; j < BK / 8; j++) {
                         const uint64_t dhi = smem_desc_k128(b_hi + j * 32), dlo = smem_desc_k128(b_lo + j * 32);
                         // small terms first, the dominant product last
+                        if(dbg & 4) continue;
                         mma_tf32_ts(d_tmem, a_lo + j * 8, dhi, idesc, (kb | j) != 0);
                         mma_tf32_ts(d_tmem, a_hi + j * 8, dlo, idesc, 1);
                         mma_tf32_ts(d_tmem, a_hi + j * 8, dhi, idesc, 1);
@@ -273,6 +298,10 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
         // ------------------------------------------------------------------ epilogue
         const int quad = warp & 3;                     // tensor-memory lanes this warp may touch
         uint32_t tile_iter = 0;
+        // identity / relu / relu6 are a clamp; with no per-row bias and no beta the whole epilogue is
+        // add, clamp, (residual, clamp,) store.  Anything else takes the general path.
+        const float2 clamp = act_clamp(p.act), post_clamp = act_clamp(p.post_act);
+        const bool epi_fast = act_is_clamp(p.act) && act_is_clamp(p.post_act) && p.bias_mode != DLP_GEMM_BIAS_M && p.beta == 0.0f;
         for(long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tile_iter++) {
             const uint32_t acc = tile_iter & 1;
             const long long m_tile = tile / n_tiles;
@@ -282,6 +311,11 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             __syncwarp();
             if(!__all_sync(0xffffffffu, mbar_wait(&sh->acc_full[acc], (tile_iter >> 1) & 1, sh, status, ST_EPI_ACC))) break;
             tc_fence_after();
+            // Everything that does not depend on the column is hoisted out of the store loop: the
+            // epilogue has to drain 128 x BN values per tile with only four warps.
+            const long long col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : 1ll;
+            float *y_row = p.y + r.out + (long long)n0 * col_stride;
+            const float *res_row = p.residual ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
             #pragma unroll 1
             for(int c = 0; c < BN / 32; c++) {
                 uint32_t v[32];
@@ -294,13 +328,26 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                     __syncwarp();
                     if(lane == 0) mbar_arrive(&sh->acc_empty[acc]);
                 }
-                if(r.valid) {
-                    #pragma unroll
-                    for(int j = 0; j < 32; j++) {
-                        const int col = n0 + c * 32 + j;
-                        if(col < p.cols)
-                            p.y[out_index(p, r, col)] = finish_output(p, r, row, col, __uint_as_float(v[j]));
+                const int col0 = n0 + c * 32;
+                const int ncols = p.cols - col0;           // columns of this chunk inside the matrix
+                if(!r.valid || ncols <= 0 || (dbg & 2)) continue;
+                float *y0 = y_row + (long long)(c * 32) * col_stride;
+                if(epi_fast && ncols >= 32) {
+                    const float *b0 = p.bias + col0;
+                    if(res_row) {
+                        const float *r0 = res_row + (long long)(c * 32) * col_stride;
+                        if(p.bias_mode == DLP_GEMM_BIAS_N) store_chunk<true, true>(v, y0, r0, col_stride, b0, clamp, p.residual_scale, post_clamp);
+                        else store_chunk<false, true>(v, y0, r0, col_stride, b0, clamp, p.residual_scale, post_clamp);
                     }
+                    else {
+                        if(p.bias_mode == DLP_GEMM_BIAS_N) store_chunk<true, false>(v, y0, nullptr, col_stride, b0, clamp, 0.0f, post_clamp);
+                        else store_chunk<false, false>(v, y0, nullptr, col_stride, b0, clamp, 0.0f, post_clamp);
+                    }
+                }
+                else {
+                    #pragma unroll 4
+                    for(int j = 0; j < 32; j++)
+                        if(j < ncols) p.y[out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, __uint_as_float(v[j]));
                 }
             }
         }
@@ -330,7 +377,7 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                 const float *src = p.a + r.base + (long long)k0 * p.a_k_stride;
                 #pragma unroll
                 for(int i = 0; i < BK; i++) {
-                    const bool ok = r.valid && (k0 + i) < p.k;
+                    const bool ok = r.valid && (k0 + i) < p.k && !(dbg & 1);
                     buf[i] = ok ? __ldg(src + (long long)i * p.a_k_stride) : 0.0f;
                 }
             }
@@ -499,7 +546,7 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const CUtensorMap 
     int *status = device_status_word();
     if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
     tc::contraction_tf32x3_kernel<BN><<<grid, tc::NUM_THREADS, smem, stream>>>(map, p, L.n_pad, L.k_pad / tc::BK, n_tiles, num_tiles,
-                                                                              status);
+                                                                              status, getenv("DLP_DBG") ? atoi(getenv("DLP_DBG")) : 0);
     DLP_LAUNCH_OK("contraction_tf32x3_kernel");
     return DLP_OK;
 }
