@@ -219,8 +219,8 @@ class Conv2DForward:
                                                   x.shape[0], x.shape[2], x.shape[3], _stream(stream)))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dlp_conv2d_fwd_destroy(self.h)
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.dlp_conv2d_fwd_destroy(self.h)
             self.h = None
 
 
@@ -251,8 +251,8 @@ class Gemm:
                                              ldc, float(beta), _ptr(ws), ws_bytes, _stream(stream)))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dlp_gemm_destroy(self.h)
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.dlp_gemm_destroy(self.h)
             self.h = None
 
 
@@ -289,8 +289,8 @@ class IPForward:
         check(lib().dlp_ip_fwd_enqueue_packed(self.h, _ptr(x), _ptr(packed), _ptr(bias), _ptr(y), x.shape[0], _stream(stream)))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().dlp_ip_fwd_destroy(self.h)
+        if getattr(self, "h", None) and _lib is not None:
+            _lib.dlp_ip_fwd_destroy(self.h)
             self.h = None
 
 

@@ -1,0 +1,247 @@
+// Plain-C face of the host library (include/dlp_host.h): catches the C++ exceptions at the
+// boundary and keeps the message for the calling thread.
+#include <dlp_host.h>
+#include <dlprim/net.hpp>
+#include <dlprim/json.hpp>
+#include <dlprim/ops/conv2d.hpp>
+#include <dlprim/ops/inner_product.hpp>
+
+#include <cstdio>
+#include <cstring>
+#include <typeinfo>
+
+using namespace dlprim;
+
+namespace {
+thread_local std::string t_err;
+
+char const *class_of(std::exception const &e)
+{
+    if(dynamic_cast<NotImplementedError const *>(&e)) return "NotImplementedError";
+    if(dynamic_cast<ValidationError const *>(&e)) return "ValidationError";
+    if(dynamic_cast<DeviceError const *>(&e)) return "DeviceError";
+    if(dynamic_cast<Error const *>(&e)) return "Error";
+    return "exception";
+}
+int write_shape(Shape const &s, int *dims)
+{
+    for(int i = 0; i < s.size(); i++) dims[i] = int(s[i]);
+    return s.size();
+}
+std::vector<Shape> read_shapes(int n, int const *ranks, int const *dims)
+{
+    std::vector<Shape> r;
+    int pos = 0;
+    for(int i = 0; i < n; i++) {
+        r.push_back(Shape::from_range(dims + pos, dims + pos + ranks[i]));
+        pos += ranks[i];
+    }
+    return r;
+}
+} // namespace
+
+#define GUARD_BEGIN try {
+#define GUARD_END(fail) } catch(std::exception const &e) { t_err = std::string(class_of(e)) + ": " + e.what(); return fail; }
+
+struct dlp_op {
+    Context ctx;
+    std::unique_ptr<Operator> op;
+    std::vector<TensorSpecs> in_specs, out_specs, par_specs;
+    size_t ws = 0;
+    std::string kernel;
+    dlp_op(int device) : ctx(Context::cuda, 0, device) {}
+    void describe()
+    {
+        kernel.clear();
+        if(Convolution2D *c = dynamic_cast<Convolution2D *>(op.get())) kernel = std::string(c->algo()) + " " + c->kernel_name();
+        else if(InnerProduct *p = dynamic_cast<InnerProduct *>(op.get())) kernel = p->kernel_name();
+    }
+};
+
+struct dlp_net {
+    Context ctx;
+    Net net;
+    std::vector<std::string> plan;
+    dlp_net(int device) : ctx(Context::cuda, 0, device), net(ctx) {}
+};
+
+extern "C" {
+
+const char *dlp_host_last_error(void) { return t_err.c_str(); }
+
+int dlp_op_create(const char *type, const char *options_json, int device, int n_inputs, const int *ranks, const int *dims, dlp_op **out)
+{
+    GUARD_BEGIN
+    std::unique_ptr<dlp_op> h(new dlp_op(device));
+    json::value opts = json::parse(options_json);
+    h->op = create_by_name(h->ctx, type, opts);
+    for(Shape const &s : read_shapes(n_inputs, ranks, dims)) h->in_specs.push_back(TensorSpecs(s, float_data));
+    h->op->setup(h->in_specs, h->out_specs, h->par_specs, h->ws);
+    h->describe();
+    *out = h.release();
+    return 0;
+    GUARD_END(1)
+}
+void dlp_op_destroy(dlp_op *op) { delete op; }
+int dlp_op_num_outputs(const dlp_op *op) { return int(op->out_specs.size()); }
+int dlp_op_num_params(const dlp_op *op) { return int(op->par_specs.size()); }
+int dlp_op_output_shape(const dlp_op *op, int i, int *dims) { return write_shape(op->out_specs.at(i).shape(), dims); }
+int dlp_op_param_shape(const dlp_op *op, int i, int *dims) { return write_shape(op->par_specs.at(i).shape(), dims); }
+size_t dlp_op_workspace(const dlp_op *op) { return op->ws; }
+const char *dlp_op_kernel(const dlp_op *op) { return op->kernel.c_str(); }
+
+int dlp_op_reshape(dlp_op *op, int n_inputs, const int *ranks, const int *dims)
+{
+    GUARD_BEGIN
+    std::vector<Shape> in = read_shapes(n_inputs, ranks, dims), out;
+    op->op->reshape(in, out, op->ws);
+    for(size_t i = 0; i < in.size(); i++) op->in_specs.at(i) = TensorSpecs(in[i], op->in_specs[i].dtype());
+    for(size_t i = 0; i < out.size(); i++) op->out_specs.at(i) = TensorSpecs(out[i], op->out_specs[i].dtype());
+    op->describe();
+    return 0;
+    GUARD_END(1)
+}
+
+int dlp_op_forward(dlp_op *op, void *const *in_ptrs, void *const *par_ptrs, void *const *out_ptrs, void *ws_ptr, void *stream)
+{
+    GUARD_BEGIN
+    std::vector<Tensor> in, out, par;
+    for(size_t i = 0; i < op->in_specs.size(); i++) in.push_back(Tensor(in_ptrs[i], 0, op->in_specs[i].shape(), op->in_specs[i].dtype()));
+    for(size_t i = 0; i < op->out_specs.size(); i++) out.push_back(Tensor(out_ptrs[i], 0, op->out_specs[i].shape(), op->out_specs[i].dtype()));
+    for(size_t i = 0; i < op->par_specs.size(); i++) par.push_back(Tensor(par_ptrs[i], 0, op->par_specs[i].shape(), op->par_specs[i].dtype()));
+    Tensor ws = op->ws > 0 ? Tensor(ws_ptr, 0, Shape(op->ws), uint8_data) : Tensor();
+    ExecutionContext e(static_cast<cudaStream_t>(stream));
+    op->op->forward(in, out, par, ws, e);
+    return 0;
+    GUARD_END(1)
+}
+
+int dlp_net_create(const char *net_json, int device, int flags, dlp_net **out)
+{
+    GUARD_BEGIN
+    std::unique_ptr<dlp_net> h(new dlp_net(device));
+    h->net.mode(CalculationsMode::predict);
+    h->net.keep_intermediate_tensors((flags & 1) != 0);
+    h->net.fuse_operators((flags & 2) == 0);
+    h->net.use_cuda_graph((flags & 4) == 0);
+    h->net.load_from_json(json::parse(net_json));
+    h->net.setup();
+    h->plan = h->net.describe_plan();
+    *out = h.release();
+    return 0;
+    GUARD_END(1)
+}
+void dlp_net_destroy(dlp_net *net) { delete net; }
+int dlp_net_num_params(const dlp_net *net) { return int(const_cast<dlp_net *>(net)->net.params().size()); }
+int dlp_net_param_name(const dlp_net *net, int index, char *buf, int n)
+{
+    GUARD_BEGIN
+    auto &m = const_cast<dlp_net *>(net)->net.params();
+    if(index < 0 || size_t(index) >= m.size()) throw ValidationError("parameter index out of range");
+    auto it = m.begin();
+    std::advance(it, index);
+    snprintf(buf, n, "%s", it->first.c_str());
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_param_shape(dlp_net *net, const char *name, int *dims)
+{
+    GUARD_BEGIN
+    return write_shape(net->net.param(name).shape(), dims);
+    GUARD_END(-1)
+}
+int dlp_net_tensor_shape(dlp_net *net, const char *name, int *dims)
+{
+    GUARD_BEGIN
+    return write_shape(net->net.tensor(name).shape(), dims);
+    GUARD_END(-1)
+}
+int dlp_net_set_param(dlp_net *net, const char *name, const float *data, size_t count)
+{
+    GUARD_BEGIN
+    Tensor &t = net->net.param(name);
+    if(t.shape().total_size() != count) throw ValidationError(std::string("size mismatch for parameter ") + name);
+    memcpy(t.host_data(), data, t.memory_size());
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_upload_params(dlp_net *net)
+{
+    GUARD_BEGIN
+    net->net.copy_parameters_to_device();
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_load_params_file(dlp_net *net, const char *path)
+{
+    GUARD_BEGIN
+    net->net.load_parameters(std::string(path));
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_save_params_file(dlp_net *net, const char *path)
+{
+    GUARD_BEGIN
+    net->net.save_parameters(path);
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_set_tensor(dlp_net *net, const char *name, const float *data, size_t count, void *stream)
+{
+    GUARD_BEGIN
+    Tensor &t = net->net.tensor(name);
+    if(t.shape().total_size() != count) throw ValidationError(std::string("size mismatch for tensor ") + name);
+    t.to_device(ExecutionContext(static_cast<cudaStream_t>(stream)), const_cast<float *>(data), false);
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_get_tensor(dlp_net *net, const char *name, float *data, size_t count, void *stream)
+{
+    GUARD_BEGIN
+    Tensor &t = net->net.tensor(name);
+    if(t.shape().total_size() != count) throw ValidationError(std::string("size mismatch for tensor ") + name);
+    t.to_host(ExecutionContext(static_cast<cudaStream_t>(stream)), data, false);
+    return 0;
+    GUARD_END(1)
+}
+void *dlp_net_tensor_device_ptr(dlp_net *net, const char *name)
+{
+    GUARD_BEGIN
+    return net->net.tensor(name).device_ptr();
+    GUARD_END(nullptr)
+}
+int dlp_net_reshape_input(dlp_net *net, const char *name, int rank, const int *dims)
+{
+    GUARD_BEGIN
+    net->net.reshape_input(name, Shape::from_range(dims, dims + rank));
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_reshape(dlp_net *net)
+{
+    GUARD_BEGIN
+    net->net.reshape();
+    net->plan = net->net.describe_plan();
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_forward(dlp_net *net, void *stream, int sync)
+{
+    GUARD_BEGIN
+    net->net.forward(ExecutionContext(static_cast<cudaStream_t>(stream)), sync != 0);
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_num_steps(const dlp_net *net) { return int(net->plan.size()); }
+int dlp_net_step_description(const dlp_net *net, int index, char *buf, int n)
+{
+    if(index < 0 || size_t(index) >= net->plan.size()) return 1;
+    snprintf(buf, n, "%s", net->plan[index].c_str());
+    return 0;
+}
+size_t dlp_net_activation_bytes(const dlp_net *net, int without_reuse)
+{
+    return without_reuse ? net->net.activation_memory_without_reuse() : net->net.activation_memory();
+}
+
+} // extern "C"

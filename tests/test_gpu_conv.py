@@ -1,0 +1,238 @@
+"""GPU parity of the convolution forward path, through the C ABI and through the factory-made
+Convolution2D operator, against the golden vectors and the CPU checker."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import reference_tolerance, small_frac
+from gpu_util import DEV, REL_TOL, kaiming, pair, rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_conv(opt, x, w, b):
+    from oracle import bindings as ob
+    return ob.conv2d(x, w, b, stride=opt.get("stride", 1), pad=opt.get("pad", 0), dilate=opt.get("dilate", 1),
+                     groups=opt.get("groups", 1), activation=opt.get("activation", "identity"))
+
+
+def run_operator(opt, x, params):
+    from dlprimitives_b200 import hostapi
+    op = hostapi.Operator("Convolution2D", opt, [x.shape])
+    out, = op.forward([to_dev(x)], [to_dev(p) for p in params])
+    torch.cuda.synchronize()
+    return op, out.cpu().numpy()
+
+
+@pytest.mark.parametrize("algo", ["", "gemm", "winograd", "depthwise_separable"])
+def test_golden_conv2d_cases(golden, algo):
+    """The reference's conv2d / conv2d_gemm / conv2d_win / conv2d_dsc sweeps: every embedded case."""
+    n = 0
+    worst = 0.0
+    for opt, params, ins, outs, eps in golden.embedded("conv2d"):
+        opt = dict(opt)
+        if algo:
+            opt["fwd_algo"] = algo
+        op, y = run_operator(opt, ins[0], params)
+        assert y.shape == outs[0].shape
+        err = rel_err(y, outs[0])
+        worst = max(worst, err)
+        assert err <= REL_TOL, (opt, op.kernel, err)
+        # the reference's own bound, eps * max(1, sigma), loosened by the 3xTF32 rounding headroom
+        assert np.abs(y - outs[0]).max() <= 4 * reference_tolerance(outs[0], eps), (opt, op.kernel)
+        n += 1
+    assert n >= 100
+    print("worst normalised error", worst)
+
+
+def test_reference_sweep_large_shapes_bit_exact_on_small_frac(golden):
+    """The cases the reference checks against its CPU operator ("use_cpu_reference"), with its
+    "small_frac" inputs (multiples of 0.5): every product and partial sum is exact in fp32, so the
+    GPU result must equal the CPU checker's bit for bit whatever the summation order."""
+    from oracle import bindings as ob
+    ob.set_threads(16)
+    rng = np.random.default_rng(21)
+    seen = 0
+    for opt, param_shapes, in_shapes, out_shapes, params in golden.checker_only("conv2d"):
+        shape = list(in_shapes[0])
+        if shape[0] * shape[1] * shape[2] * shape[3] > 3_000_000:
+            shape[0] = max(1, 3_000_000 // (shape[1] * shape[2] * shape[3]))    # bound the CPU checker's time
+        x = small_frac(rng, shape)
+        ps = [small_frac(rng, s) for s in param_shapes]
+        b = ps[1] if opt.get("bias", True) else None
+        want = oracle_conv(opt, x, ps[0], b)
+        op, got = run_operator(opt, x, ps)
+        assert got.shape == want.shape
+        assert np.array_equal(got, want), (opt, shape, op.kernel, np.abs(got - want).max())
+        seen += 1
+    assert seen >= 100
+
+
+CONFIG_SHAPES = [
+    # (name, N, Cin, H, Cout, k, stride, pad, groups, bias, act)
+    ("cfg1_3x3_64_56", 16, 64, 56, 64, 3, 1, 1, 1, True, "relu"),
+    ("cfg2_1x1_256_1024", 64, 256, 14, 1024, 1, 1, 0, 1, True, "identity"),
+    ("cfg2_1x1_1024_256", 64, 1024, 14, 256, 1, 1, 0, 1, True, "identity"),
+    ("cfg2_1x1_512_2048", 64, 512, 14, 2048, 1, 1, 0, 1, True, "identity"),
+    ("cfg4_3x3_64_56", 64, 64, 56, 64, 3, 1, 1, 1, False, "identity"),
+    ("cfg4_3x3_128_28", 64, 128, 28, 128, 3, 1, 1, 1, False, "identity"),
+    ("cfg4_3x3_256_14", 64, 256, 14, 256, 3, 1, 1, 1, False, "identity"),
+    ("cfg4_3x3_512_7", 64, 512, 7, 512, 3, 1, 1, 1, False, "identity"),
+    ("resnet_stem_7x7", 8, 3, 224, 64, 7, 2, 3, 1, True, "relu"),
+    ("resnet_3x3_s2", 16, 128, 56, 128, 3, 2, 1, 1, True, "relu"),
+    ("resnet_1x1_s2", 16, 256, 56, 512, 1, 2, 0, 1, True, "identity"),
+]
+
+
+@pytest.mark.parametrize("cfg", CONFIG_SHAPES, ids=[c[0] for c in CONFIG_SHAPES])
+def test_config_shapes_full_size(cfg):
+    """The benchmark configurations at their full sizes against the CPU checker; the batch the CPU
+    side computes is capped (images are independent) so each case stays within seconds."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    ob.set_threads(16)
+    name, N, cin, H, cout, k, stride, pad, groups, bias, act = cfg
+    rng = np.random.default_rng(hash(name) % 2**31)
+    x = rng.standard_normal((N, cin, H, H), dtype=np.float32)
+    w = kaiming(rng, (cout, cin // groups, k, k))
+    b = (rng.uniform(-0.1, 0.1, cout).astype(np.float32) if name.startswith("cfg1") else np.zeros(cout, np.float32)) if bias else None
+    plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, stride=stride, pad=pad, groups=groups, batch=N, height=H,
+                              width=H, bias=bias, activation=act)
+    xd, wd, bd = to_dev(x), to_dev(w), to_dev(b)
+    y = torch.full(plan.output_shape(N), float("nan"), device=DEV)
+    ws = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=DEV)
+    plan.enqueue(xd, wd, bd, y, ws)
+    assert capi.device_status() == 0
+    got = y.cpu().numpy()
+    assert not np.isnan(got).any()
+    cpu_images = min(N, 8)
+    sel = np.linspace(0, N - 1, cpu_images).astype(int)          # first, last and some in between
+    want = ob.conv2d(x[sel], w, b, stride=stride, pad=pad, groups=groups, activation=act)
+    err = rel_err(got[sel], want)
+    assert err <= REL_TOL, (plan.kernel(), err)
+    # a cheap whole-batch property: every image of the batch gives the same result as when it runs alone
+    y1 = torch.empty(plan.output_shape(1), device=DEV)
+    for i in (0, N - 1):
+        plan.enqueue(xd[i:i + 1].contiguous(), wd, bd, y1, ws)
+        assert torch.equal(y1[0], y[i])
+
+
+def test_depthwise_mobilenet_rows():
+    """Config 3: the depthwise layers of MobileNetV2 (stride 1 and 2) followed by their pointwise
+    1x1 convolution with ReLU6, N = 128, compared on a subset of the images."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    ob.set_threads(16)
+    rows = [(32, 112, 1, 16), (96, 112, 2, 24), (144, 56, 1, 24), (144, 56, 2, 32), (192, 28, 1, 32), (192, 28, 2, 64),
+            (384, 14, 1, 64), (384, 14, 1, 96), (576, 14, 1, 96), (576, 14, 2, 160), (960, 7, 1, 160), (960, 7, 1, 320)]
+    rng = np.random.default_rng(33)
+    for C, H, stride, cout in rows:
+        N = 128 if C * H * H <= 150_000 else 32           # keep the biggest layers within a few hundred MB
+        x = rng.standard_normal((N, C, H, H), dtype=np.float32)
+        wd_ = (rng.standard_normal((C, 1, 3, 3)) * np.sqrt(2.0 / 9)).astype(np.float32)
+        wp = kaiming(rng, (cout, C, 1, 1))
+        dw = capi.Conv2DForward(channels_in=C, channels_out=C, kernel=3, stride=stride, pad=1, groups=C, batch=N, height=H, width=H,
+                                bias=False, activation="identity")
+        assert dw.algo() == "depthwise_separable" and dw.kernel() == "depthwise_k3_s%d" % stride
+        mid = torch.empty(dw.output_shape(N), device=DEV)
+        dw.enqueue(to_dev(x), to_dev(wd_), None, mid, None)
+        OH = mid.shape[2]
+        pw = capi.Conv2DForward(channels_in=C, channels_out=cout, kernel=1, batch=N, height=OH, width=OH, bias=False, activation="relu6")
+        out = torch.empty(pw.output_shape(N), device=DEV)
+        ws = torch.empty(max(pw.workspace(), 16), dtype=torch.uint8, device=DEV)
+        pw.enqueue(mid, to_dev(wp), None, out, ws)
+        assert capi.device_status() == 0
+        sel = [0, N // 2, N - 1]
+        want_mid = ob.conv2d(x[sel], wd_, None, stride=stride, pad=1, groups=C)
+        want = ob.conv2d(want_mid, wp, None, activation="relu6")
+        assert rel_err(mid.cpu().numpy()[sel], want_mid) <= 1e-5, (C, H, stride)     # plain fp32 FMA path
+        assert rel_err(out.cpu().numpy()[sel], want) <= REL_TOL, (C, H, stride, cout)
+
+
+def test_enqueue_contract():
+    """y = factor*y + act(conv + bias); y is not read when factor == 0; a smaller batch than planned
+    is accepted; every activation; all three kernel families."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    rng = np.random.default_rng(5)
+    cases = [dict(groups=1, math_mode=capi.MATH_AUTO), dict(groups=1, math_mode=capi.MATH_FP32_FFMA), dict(groups=2, math_mode=capi.MATH_AUTO),
+             dict(groups=12, math_mode=capi.MATH_AUTO)]
+    for case in cases:
+        g = case["groups"]
+        for act in ("identity", "relu", "tanh", "sigmoid", "relu6"):
+            x = rng.standard_normal((3, 12, 10, 9), dtype=np.float32)
+            w = kaiming(rng, (12, 12 // g, 3, 3)) * 3
+            b = rng.uniform(-1, 1, 12).astype(np.float32)
+            plan = capi.Conv2DForward(channels_in=12, channels_out=12, kernel=3, pad=1, groups=g, batch=5, height=10, width=9, bias=True,
+                                      activation=act, math_mode=case["math_mode"])
+            ws = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=DEV)
+            want = ob.conv2d(x, w, b, pad=1, groups=g, activation=act)
+            y = torch.full(plan.output_shape(3), float("nan"), device=DEV)
+            plan.enqueue(to_dev(x), to_dev(w), to_dev(b), y, ws, factor=0.0)
+            assert rel_err(y.cpu().numpy(), want) <= REL_TOL, (case, act, plan.kernel())
+            y0 = rng.standard_normal(want.shape).astype(np.float32)
+            y = to_dev(y0)
+            plan.enqueue(to_dev(x), to_dev(w), to_dev(b), y, ws, factor=0.5)
+            assert rel_err(y.cpu().numpy(), 0.5 * y0 + want) <= REL_TOL, (case, act, plan.kernel())
+    assert capi.device_status() == 0
+
+
+def test_fused_residual_matches_conv_then_elementwise():
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((4, 64, 14, 14), dtype=np.float32)
+    w = kaiming(rng, (256, 64, 1, 1))
+    b = rng.uniform(-0.1, 0.1, 256).astype(np.float32)
+    res = rng.standard_normal((4, 256, 14, 14), dtype=np.float32)
+    plan = capi.Conv2DForward(channels_in=64, channels_out=256, kernel=1, batch=4, height=14, width=14, bias=True, activation="identity")
+    packed = plan.prepack(to_dev(w))
+    y = torch.empty(plan.output_shape(4), device=DEV)
+    plan.enqueue_packed(to_dev(x), packed, to_dev(b), y, residual=to_dev(res), residual_scale=1.0, post_activation="relu")
+    want = ob.elementwise(ob.conv2d(x, w, b), res, "sum", 1.0, 1.0, "relu")
+    assert rel_err(y.cpu().numpy(), want) <= REL_TOL
+    # in place: the residual buffer is also the output
+    r = to_dev(res)
+    plan.enqueue_packed(to_dev(x), packed, to_dev(b), r, residual=r, residual_scale=0.5, post_activation="identity")
+    want = ob.elementwise(ob.conv2d(x, w, b), res, "sum", 1.0, 0.5, "identity")
+    assert rel_err(r.cpu().numpy(), want) <= REL_TOL
+
+
+def test_algorithm_selection_follows_the_reference_rules():
+    """src/core/conv.cpp:672-729: "depthwise_separable" and "winograd" requests that are not
+    eligible fall back to "gemm"; the selection strings are the reference's."""
+    from dlprimitives_b200 import capi
+    mk = lambda **kw: capi.Conv2DForward(batch=2, height=16, width=16, **kw)
+    assert mk(channels_in=16, channels_out=16, kernel=3, pad=1, groups=16).algo() == "depthwise_separable"
+    assert mk(channels_in=16, channels_out=16, kernel=3, pad=1, groups=16, algo="gemm").algo() == "gemm"
+    assert mk(channels_in=16, channels_out=16, kernel=3, pad=1, groups=16, stride=2).algo() == "depthwise_separable"   # native stride 2
+    assert mk(channels_in=16, channels_out=16, kernel=3, pad=1, groups=16, stride=2, algo="depthwise_separable").algo() == "gemm"
+    assert mk(channels_in=16, channels_out=32, kernel=3, pad=1, groups=16).algo() == "gemm"     # channel multiplier: not handled as depthwise
+    assert mk(channels_in=16, channels_out=16, kernel=3, pad=0, algo="winograd").algo() == "gemm"
+    assert mk(channels_in=16, channels_out=16, kernel=1).algo() == "gemm"
+    assert mk(channels_in=16, channels_out=16, kernel=1).kernel().startswith("igemm_tf32x3")
+    assert mk(channels_in=16, channels_out=16, kernel=3, groups=2).kernel().startswith("igemm_ffma")
+
+
+def test_errors_are_reported_not_swallowed():
+    from dlprimitives_b200 import capi, hostapi
+    plan = capi.Conv2DForward(channels_in=8, channels_out=8, kernel=3, pad=1, batch=2, height=8, width=8, bias=True)
+    x = torch.zeros(2, 8, 8, 8, device=DEV)
+    w = torch.zeros(8, 8, 3, 3, device=DEV)
+    y = torch.zeros(2, 8, 8, 8, device=DEV)
+    ws = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=DEV)
+    with pytest.raises(capi.ValidationError):
+        plan.enqueue(x, w, None, y, ws)                            # the plan has a bias, none given
+    with pytest.raises(capi.ValidationError):
+        plan.enqueue(torch.zeros(2, 8, 9, 8, device=DEV), w, torch.zeros(8, device=DEV), y, ws)   # height differs from the plan
+    if plan.workspace() > 0:
+        with pytest.raises(capi.ValidationError):
+            plan.enqueue(x, w, torch.zeros(8, device=DEV), y, None)    # workspace missing
+    with pytest.raises(hostapi.HostError) as e:
+        hostapi.Operator("Convolution2D", {"channels_in": 4, "channels_out": 8, "kernel": 3}, [(1, 5, 8, 8)])   # channel mismatch
+    assert e.value.kind == "ValidationError"
+    with pytest.raises(hostapi.HostError) as e:
+        hostapi.Operator("NoSuchOperator", {}, [(1, 5, 8, 8)])
+    assert e.value.kind == "ValidationError"
+    # empty batch: nothing to do, no launch, no error
+    plan.enqueue(torch.zeros(0, 8, 8, 8, device=DEV), w, torch.zeros(8, device=DEV), torch.zeros(0, 8, 8, 8, device=DEV), ws)

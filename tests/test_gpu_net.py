@@ -1,0 +1,134 @@
+"""GPU parity of whole-network inference: dlprim::Net on the CUDA context against the reference's
+own Net on its CPU context (committed outputs, and live when the reference CPU build is present)."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT
+from gpu_util import DEV, REL_TOL, rel_err
+
+pytestmark = pytest.mark.gpu
+
+_spec = importlib.util.spec_from_file_location("make_net_golden", os.path.join(ROOT, "tests", "golden", "make_net_golden.py"))
+net_golden = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(net_golden)
+
+
+def build_gpu_net(net_json, params, flags=0):
+    from dlprimitives_b200 import hostapi
+    net = hostapi.Net(net_json, flags=flags)
+    assert set(net.param_names()) == set(params)
+    for name, value in params.items():
+        assert net.param_shape(name) == value.shape
+        net.set_param(name, value)
+    net.upload_params()
+    return net
+
+
+def run_gpu(net, x, outputs=("fc", "prob"), repeats=3):
+    """Several forwards on a side stream: eager first, then graph capture, then replay."""
+    stream = torch.cuda.Stream()
+    results = []
+    xh = torch.from_numpy(x).pin_memory()
+    with torch.cuda.stream(stream):
+        for _ in range(repeats):
+            net.set_tensor("data", xh, stream)
+            net.forward(stream)
+            outs = {name: torch.empty(net.tensor_shape(name)).pin_memory() for name in outputs}
+            for name, t in outs.items():
+                net.get_tensor(name, t, stream)
+            stream.synchronize()
+            results.append({k: v.numpy().copy() for k, v in outs.items()})
+    return results
+
+
+@pytest.mark.parametrize("case", list(net_golden.CASES))
+@pytest.mark.parametrize("flags", [0, 2, 1 | 4], ids=["fused+graph", "unfused+graph", "keep_intermediate+eager"])
+def test_small_resnet_against_reference_cpu_outputs(case, flags):
+    from dlprimitives_b200 import capi, resnet50
+    batch, h, w, folded, div, pseed, iseed = net_golden.CASES[case]
+    net_json = resnet50.make_json(batch, h, w, folded=folded, width_div=div)
+    params = resnet50.make_params(net_json, seed=pseed)
+    x = resnet50.make_input(net_json, seed=iseed)
+    golden = np.load(os.path.join(ROOT, "tests", "golden", "net_cases.npz"))
+    net = build_gpu_net(net_json, params, flags)
+    plan = net.plan()
+    fused = [line for line in plan if "+residual" in line]
+    if flags == 0 and folded:
+        assert len(fused) == 16, plan             # every bottleneck's sum is folded into a convolution
+        assert not any(" Elementwise" in line for line in plan)
+    else:
+        assert not fused or not folded
+    results = run_gpu(net, x)
+    for r in results:                               # eager, captured and replayed runs agree exactly
+        assert np.array_equal(r["fc"], results[0]["fc"])
+    assert rel_err(results[0]["fc"], golden[case + "_fc"]) <= REL_TOL
+    assert np.abs(results[0]["prob"] - golden[case + "_prob"]).max() <= 1e-4     # the reference scripts' bar
+    assert (results[0]["prob"].argmax(1) == golden[case + "_prob"].argmax(1)).all()
+    assert capi.device_status() == 0
+    if flags == 0:
+        assert net.activation_bytes() < net.activation_bytes(without_reuse=True)
+
+
+def test_resnet50_full_size_rows_against_reference_cpu():
+    """Config 5 at its real size on the GPU (3x224x224, full channel widths, a batch of 32); the
+    reference's CPU Net computes four of those images (it handles images independently), which keeps
+    the CPU side to about half a minute."""
+    from oracle import bindings as ob
+    if not ob.ref_available():
+        pytest.skip("reference CPU build (oracle/_ref) not present")
+    from dlprimitives_b200 import capi, resnet50
+    batch = 32
+    net_json = resnet50.make_json(batch)
+    params = resnet50.make_params(net_json, seed=0)
+    x = resnet50.make_input(net_json, seed=1)
+    net = build_gpu_net(net_json, params)
+    got = run_gpu(net, x, repeats=2)[-1]
+    sel = [0, 13, 31]
+    ref_json = resnet50.make_json(len(sel))
+    ref = ob.RefNet(ref_json)
+    for name in ref.param_names():
+        ref.set_param(name, params[name])
+    ref.set_tensor("data", x[sel])
+    ref.forward()
+    want_fc, want_prob = ref.get_tensor("fc"), ref.get_tensor("prob")
+    assert rel_err(got["fc"][sel], want_fc) <= REL_TOL
+    assert np.abs(got["prob"][sel] - want_prob).max() <= 1e-4
+    assert (got["prob"][sel].argmax(1) == want_prob.argmax(1)).all()
+    assert capi.device_status() == 0
+
+
+def test_reshape_to_smaller_and_larger_batch():
+    from dlprimitives_b200 import resnet50
+    net_json = resnet50.make_json(4, 64, 64, width_div=8)
+    params = resnet50.make_params(net_json, seed=3)
+    net = build_gpu_net(net_json, params)
+    x = np.random.default_rng(8).standard_normal((6, 3, 64, 64), dtype=np.float32)
+    full = None
+    for b in (4, 2, 6):
+        net.reshape_input("data", (b, 3, 64, 64))
+        net.reshape()
+        assert net.tensor_shape("prob") == (b, 1000)
+        out = run_gpu(net, np.ascontiguousarray(x[:b]), repeats=2)[-1]["fc"]
+        if full is None:
+            full = out
+        n = min(b, 4)
+        assert np.array_equal(out[:n], full[:n])    # per-image results do not depend on the batch
+
+
+def test_parameter_file_round_trip(tmp_path):
+    from dlprimitives_b200 import resnet50
+    net_json = resnet50.make_json(2, 64, 64, width_div=8)
+    params = resnet50.make_params(net_json, seed=3)
+    x = resnet50.make_input(net_json, seed=4)
+    a = build_gpu_net(net_json, params)
+    path = str(tmp_path / "weights.dlp")
+    a.save_params_file(path)
+    assert open(path, "rb").read(4) == b"DLPW"
+    from dlprimitives_b200 import hostapi
+    b = hostapi.Net(net_json)
+    b.load_params_file(path)
+    assert np.array_equal(run_gpu(a, x, repeats=1)[0]["fc"], run_gpu(b, x, repeats=1)[0]["fc"])
