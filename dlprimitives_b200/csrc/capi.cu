@@ -75,8 +75,11 @@ struct dlp_conv2d_plan {
     int out_h, out_w;
     int k;                   // Cin/groups * KH * KW
     bool strided_a;          // 1x1, stride 1, no padding: the taps are a plain stride
+    bool tapblock;           // tensor-core path with channels in blocks of 32: K runs (channel block, tap, channel)
     TcPacked packed;
     KTap *ktab = nullptr;    // device, k_pad entries (gather mode)
+    int *tap_dydx = nullptr; // device, one entry per kernel tap
+    int num_taps = 0;
     int device = 0;
 };
 
@@ -191,23 +194,27 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
         // "winograd" requests land here until the Winograd kernels exist: like the reference does for
         // an incompatible request (src/core/conv.cpp:719-727), the plan substitutes the GEMM algorithm.
         plan->algo = "gemm";
-        const bool tc_ok = d.groups == 1 && d.math_mode != DLP_MATH_FP32_FFMA;
+        // the tensor-core loader keeps one validity bit per kernel tap in a 64-bit word
+        const bool tc_ok = d.groups == 1 && d.math_mode != DLP_MATH_FP32_FFMA && d.kernel[0] * d.kernel[1] <= MAX_TAPS;
         if(d.math_mode == DLP_MATH_TF32X3 && !tc_ok)
-            return fail(DLP_NOT_IMPLEMENTED, "the tensor-core kernel handles groups == 1 only");
+            return fail(DLP_NOT_IMPLEMENTED, "the tensor-core kernel handles groups == 1 and kernels of at most 63 taps");
         plan->kind = tc_ok ? CK_TC : CK_FFMA;
     }
     plan->strided_a = d.kernel[0] == 1 && d.kernel[1] == 1 && d.stride[0] == 1 && d.stride[1] == 1 && d.pad[0] == 0 && d.pad[1] == 0;
 
+    plan->tapblock = plan->kind == CK_TC && !plan->strided_a && d.channels_in % 32 == 0;
     if(plan->kind != CK_DEPTHWISE) {
         plan->packed = tc_packed_layout(d.channels_out / d.groups, plan->k);
         if(plan->kind == CK_TC)
-            plan->kernel = std::string("igemm_tf32x3_bn") + std::to_string(plan->packed.bn) + (plan->strided_a ? "_1x1" : "_gather");
+            plan->kernel = std::string("igemm_tf32x3_bn") + std::to_string(plan->packed.bn) + (plan->strided_a ? "_1x1" : (plan->tapblock ? "_taps" : "_gather"));
         else
             plan->kernel = std::string("igemm_ffma_64x64") + (plan->strided_a ? "_1x1" : "_gather");
         if(!plan->strided_a) {
             // tap table: k -> (c, ky, kx) in the weight tensor's own order [Cin/g][KH][KW]
             const int k_pad = plan->packed.k_pad;
             std::vector<KTap> tab(k_pad);
+            plan->num_taps = d.kernel[0] * d.kernel[1];
+            std::vector<int> taps(plan->num_taps);
             const int cin_g = d.channels_in / d.groups;
             int idx = 0;
             for(int c = 0; c < cin_g; c++)
@@ -215,14 +222,18 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
                     for(int kx = 0; kx < d.kernel[1]; kx++, idx++) {
                         const int dy = ky * d.dilate[0], dx = kx * d.dilate[1];
                         tab[idx].offset = (c * d.height + dy) * d.width + dx;
-                        tab[idx].dydx = (dy << 16) | dx;
+                        tab[idx].tap = plan->kind == CK_TC ? ky * d.kernel[1] + kx : std::min(ky * d.kernel[1] + kx, plan->num_taps - 1);
+                        taps[ky * d.kernel[1] + kx] = (dy << 16) | dx;
                     }
-            for(; idx < k_pad; idx++) { tab[idx].offset = 0; tab[idx].dydx = 0x7fff7fff; }
+            for(; idx < k_pad; idx++) { tab[idx].offset = 0; tab[idx].tap = TAP_PADDING; }
             DLP_CUDA_OK(cudaMalloc((void **)&plan->ktab, sizeof(KTap) * k_pad));
-            cudaError_t e = cudaMemcpy(plan->ktab, tab.data(), sizeof(KTap) * k_pad, cudaMemcpyHostToDevice);
+            cudaError_t e = cudaMalloc((void **)&plan->tap_dydx, sizeof(int) * taps.size());
+            if(e == cudaSuccess) e = cudaMemcpy(plan->ktab, tab.data(), sizeof(KTap) * k_pad, cudaMemcpyHostToDevice);
+            if(e == cudaSuccess) e = cudaMemcpy(plan->tap_dydx, taps.data(), sizeof(int) * taps.size(), cudaMemcpyHostToDevice);
             if(e != cudaSuccess) {
                 cudaFree(plan->ktab);
-                return check_cuda(e, "upload of the tap table");
+                if(plan->tap_dydx) cudaFree(plan->tap_dydx);
+                return check_cuda(e, "upload of the tap tables");
             }
         }
     }
@@ -234,6 +245,7 @@ void dlp_conv2d_fwd_destroy(dlp_conv2d_plan *plan)
 {
     if(!plan) return;
     if(plan->ktab) cudaFree(plan->ktab);
+    if(plan->tap_dydx) cudaFree(plan->tap_dydx);
     delete plan;
 }
 const char *dlp_conv2d_fwd_algo(const dlp_conv2d_plan *plan) { return plan ? plan->algo.c_str() : ""; }
@@ -246,7 +258,8 @@ dlp_status dlp_conv2d_fwd_prepack(const dlp_conv2d_plan *plan, const float *w, v
     DLP_REQUIRE(plan && w, "null argument");
     if(plan->kind != CK_TC) return DLP_OK;
     DLP_REQUIRE(packed != nullptr, "null packed buffer");
-    return tc_prepack(plan->packed, w, plan->k, 1, plan->d.channels_out, plan->k, static_cast<float *>(packed), (cudaStream_t)stream);
+    return tc_prepack(plan->packed, w, plan->k, 1, plan->d.channels_out, plan->k, static_cast<float *>(packed),
+                      plan->tapblock ? plan->num_taps : 0, (cudaStream_t)stream);
 }
 
 static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, const float *w_raw, const float *packed, const float *bias,
@@ -287,8 +300,11 @@ static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, cons
         p.a_k_stride = (long long)d.height * d.width;
     }
     else {
-        p.a_mode = A_GATHER;
+        p.a_mode = plan->tapblock ? A_TAPBLOCK : A_GATHER;
+        p.a_k_stride = (long long)d.height * d.width;
         p.ktab = plan->ktab;
+        p.tap_dydx = plan->tap_dydx;
+        p.num_taps = plan->num_taps;
     }
     p.b = w_raw;
     p.b_col_stride = plan->k;
@@ -316,6 +332,8 @@ dlp_status dlp_conv2d_fwd_enqueue(const dlp_conv2d_plan *plan, const float *x, c
                                   size_t ws_bytes, float factor, int batch, int in_h, int in_w, void *stream)
 {
     DLP_REQUIRE(plan != nullptr, "null plan");
+    DLP_REQUIRE(batch >= 0, "negative batch");
+    if(batch == 0) return DLP_OK;      // an empty batch is valid and launches nothing
     DLP_REQUIRE(w != nullptr, "null weights");
     const float *packed = nullptr;
     if(plan->kind == CK_TC) {
@@ -335,6 +353,8 @@ dlp_status dlp_conv2d_fwd_enqueue_packed(const dlp_conv2d_plan *plan, const floa
 {
     (void)ws; (void)ws_bytes;
     DLP_REQUIRE(plan != nullptr, "null plan");
+    DLP_REQUIRE(batch >= 0, "negative batch");
+    if(batch == 0) return DLP_OK;
     DLP_REQUIRE(packed != nullptr, "null weights");
     // plans whose kernel reads raw weights take them through the same argument
     const float *raw = plan->kind == CK_TC ? nullptr : static_cast<const float *>(packed);
@@ -406,7 +426,7 @@ dlp_status dlp_gemm_enqueue(const dlp_gemm_plan *plan, int m, int n, int k, cons
     if(plan->use_tc && k > 0) {
         const TcPacked L = tc_packed_layout(n, k);
         DLP_REQUIRE(ws != nullptr && ws_bytes >= L.bytes(), "workspace smaller than the packed B operand needs");
-        st = tc_prepack(L, b, p.b_col_stride, p.b_k_stride, n, k, static_cast<float *>(ws), (cudaStream_t)stream);
+        st = tc_prepack(L, b, p.b_col_stride, p.b_k_stride, n, k, static_cast<float *>(ws), 0, (cudaStream_t)stream);
         if(st != DLP_OK) return st;
         return launch_contraction_tc(p, L, static_cast<const float *>(ws), (cudaStream_t)stream);
     }
@@ -453,14 +473,15 @@ dlp_status dlp_ip_fwd_prepack(const dlp_ip_plan *plan, const float *w, void *pac
     DLP_REQUIRE(plan && w, "null argument");
     if(!plan->use_tc) return DLP_OK;
     DLP_REQUIRE(packed != nullptr, "null packed buffer");
-    return tc_prepack(plan->packed, w, plan->d.inputs, 1, plan->d.outputs, plan->d.inputs, static_cast<float *>(packed), (cudaStream_t)stream);
+    return tc_prepack(plan->packed, w, plan->d.inputs, 1, plan->d.outputs, plan->d.inputs, static_cast<float *>(packed), 0, (cudaStream_t)stream);
 }
 
 static dlp_status ip_enqueue(const dlp_ip_plan *plan, const float *x, const float *w_raw, const float *packed, const float *bias, float *y,
                              int batch, cudaStream_t stream)
 {
-    DLP_REQUIRE(x && y, "null tensor");
     DLP_REQUIRE(batch >= 0, "negative batch");
+    if(batch == 0) return DLP_OK;
+    DLP_REQUIRE(x && y, "null tensor");
     DLP_REQUIRE(!plan->d.bias == !bias, "bias pointer does not match the plan's bias setting");
     if(batch == 0) return DLP_OK;
     dlp_gemm_desc g;

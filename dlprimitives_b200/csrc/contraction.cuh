@@ -14,7 +14,9 @@ namespace dlp {
 
 enum : int {
     A_GATHER = 0,  // general convolution: address = row_base + ktab[k].offset, bounds-checked per tap
-    A_STRIDED = 1  // address = row_base + k * a_k_stride (1x1 stride-1 convolution, matrices)
+    A_STRIDED = 1, // address = row_base + k * a_k_stride (1x1 stride-1 convolution, matrices)
+    A_TAPBLOCK = 2 // convolution with channels in blocks of 32: k-block kb = (channel block, tap); the 32 values
+                   // of a k-block are one tap of 32 consecutive channels: row_base + tap offset + channel * a_k_stride
 };
 enum : int {
     OUT_NCHW = 0,     // row = (b, pix): y[(b * out_channels_total + col) * out_plane + pix]
@@ -22,9 +24,11 @@ enum : int {
 };
 
 struct KTap {
-    int offset;  // element offset of tap k from the row's base address: c*H*W + dy*W + dx
-    int dydx;    // (dy << 16) | dx, the tap's displacement for the bounds check; 0x7fff7fff marks padding
+    int offset;  // element offset of reduction index k from the row's base address: c*H*W + dy*W + dx
+    int tap;     // which kernel tap (ky*KW + kx) it belongs to; TAP_PADDING for the zero padding beyond K
 };
+constexpr int TAP_PADDING = 63;
+constexpr int MAX_TAPS = 63;     // kernels with more taps than bits in the per-pixel validity mask use the FFMA path
 
 struct Contraction {
     // sizes
@@ -43,6 +47,8 @@ struct Contraction {
     int stride_h, stride_w, pad_h, pad_w;
     long long a_batch_stride;  // Cin_total*H*W
     const KTap *ktab;    // k_pad entries
+    const int *tap_dydx; // num_taps entries: (dy << 16) | dx displacement of each kernel tap (dilation included)
+    int num_taps;
     // B side, raw form: B(col, k) = b[col * b_col_stride + k * b_k_stride]
     const float *b;
     long long b_col_stride, b_k_stride;
@@ -74,7 +80,8 @@ __device__ __forceinline__ RowInfo make_row(const Contraction &p, long long row)
     r.valid = row < p.rows;
     if(!r.valid) row = 0;
     if(p.plane > 0) {
-        int b = int(row / p.plane);
+        // 32-bit division when it fits: this runs once per tile in every loader and epilogue thread
+        int b = p.rows < (1ll << 31) ? int(unsigned(row) / unsigned(p.plane)) : int(row / p.plane);
         int pix = int(row - (long long)b * p.plane);
         int oy = pix / p.out_w;
         int ox = pix - oy * p.out_w;
@@ -111,14 +118,15 @@ __device__ __forceinline__ float finish_output(const Contraction &p, const RowIn
 dlp_status launch_contraction_ffma(const Contraction &p, int groups, long long a_group_stride, long long b_group_stride,
                                    int out_group_channels, cudaStream_t stream);
 
-struct TcPacked {   // pre-packed B for the tensor-core kernel: [2][n_pad][k_pad] fp32 (hi plane, lo plane)
+struct TcPacked {   // pre-packed B for the tensor-core kernel: [n_pad][k_pad] fp32, zero padded, K-major
     int bn;         // column tile: 64 or 128
     int n_pad, k_pad;
-    size_t bytes() const { return size_t(2) * n_pad * k_pad * sizeof(float); }
+    size_t bytes() const { return size_t(n_pad) * k_pad * sizeof(float); }
 };
 TcPacked tc_packed_layout(int cols, int k);
+// taps > 0 packs in the A_TAPBLOCK order: packed k = ((channel block * taps + tap) * 32 + channel in block)
 dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
-                      float *packed, cudaStream_t stream);
+                      float *packed, int taps, cudaStream_t stream);
 dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream);
 
 } // namespace dlp

@@ -49,7 +49,8 @@ contraction_ffma_kernel(Contraction p, long long a_group_stride, long long b_gro
                     v = __ldg(a + ar.base + (long long)kk * p.a_k_stride);
                 else {
                     const KTap t = p.ktab[kk];
-                    const int iy = ar.iy0 + (t.dydx >> 16), ix = ar.ix0 + (t.dydx & 0xffff);
+                    const int d = __ldg(p.tap_dydx + t.tap);
+                    const int iy = ar.iy0 + (d >> 16), ix = ar.ix0 + (d & 0xffff);
                     if(unsigned(iy) < unsigned(p.in_h) && unsigned(ix) < unsigned(p.in_w)) v = __ldg(a + ar.base + t.offset);
                 }
             }

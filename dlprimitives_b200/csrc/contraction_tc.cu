@@ -3,20 +3,25 @@
 //   D[row, col] = sum_k A(row, k) * B(col, k),   rows = output pixels, cols = output channels.
 //
 // Every fp32 operand value v is split as  hi = v with the low 13 mantissa bits cleared (exactly a
-// TF32 number) and lo = v - hi (exact in fp32).  The kernel accumulates  hi_a*hi_b + lo_a*hi_b +
-// hi_a*lo_b  in one fp32 accumulator, dropping only lo_a*lo_b (relative size 2^-22).
+// TF32 number) and lo = v - hi (exact in fp32).  The kernel accumulates  lo_a*hi_b + hi_a*lo_b +
+// hi_a*hi_b, dropping only lo_a*lo_b (relative size 2^-22).
 //
-// Data flow per CTA (persistent, one CTA per SM, 128-row x BN-column output tiles):
-//   * B (weights, pre-packed hi/lo planes, K-major, padded) : TMA -> 128B-swizzled shared memory ring
-//   * A (activations) : loader warps read the caller's NCHW tensor directly (implicit im2col, no
+// Data flow per CTA (persistent, one CTA per SM, 128-row x BN-column output tiles, K in blocks of 32):
+//   * B (weights, one zero-padded K-major plane): TMA -> 128B-swizzled shared-memory ring, several
+//     k-blocks ahead of use.  The tensor core reads only the TF32 part of each fp32 word, so a landed
+//     tile is the hi operand as it is; the loader warps write the remainder to a lo tile at the same
+//     offsets just before use.  The weights therefore cross L2 once, as plain fp32.
+//   * A (activations): loader warps read the caller's NCHW tensor directly (implicit im2col, no
 //     re-layout in memory), split each value in registers and write hi/lo with tcgen05.st into a
-//     ring of tensor-memory columns.  The MMA therefore takes A from tensor memory and B from
-//     shared memory, which keeps the shared-memory read traffic of the three products at one
-//     operand instead of two.
-//   * one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), accumulators live in tensor
-//     memory, double-buffered so the epilogue of a tile overlaps the main loop of the next one
-//   * epilogue warps read the accumulator with tcgen05.ld, apply bias / activation / residual /
-//     beta and store straight to NCHW (32 consecutive pixels per warp store) or row-major.
+//     ring of tensor-memory columns.  The MMA takes A from tensor memory and B from shared memory,
+//     which keeps the shared-memory read traffic of the three products at one operand.
+//   * one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8).
+//   * the tensor core adds into its fp32 accumulator with truncation, which over thousands of steps
+//     shows up as a systematic shrink of the result.  So a tensor-memory accumulator only ever holds
+//     the partial sum of CHUNK_KB k-blocks (two such buffers alternate); accumulate warps add the
+//     partial sums into a shared-memory tile with ordinary round-to-nearest fp32 adds, and on the
+//     tile's last chunk apply bias / activation / residual / beta and store straight to NCHW
+//     (32 consecutive pixels per warp store) or row-major.
 //
 // All mbarrier waits are bounded: a wait that gives up records a code in the device status word,
 // raises the CTA's abort flag, and every role then leaves its loop; the CTA drains its bulk copies
@@ -25,6 +30,7 @@
 #include <cuda.h>
 #include <mutex>
 #include <cstdlib>
+#include <cstdio>
 
 namespace dlp {
 
@@ -32,25 +38,37 @@ namespace tc {
 
 constexpr int BM = 128;              // rows per tile = tensor-memory lanes
 constexpr int BK = 32;               // K per pipeline stage: 32 fp32 = one 128-byte swizzle row
-constexpr int STAGES = 4;
-constexpr int A_COL_BASE = 256;      // tensor-memory columns [0,256) hold two accumulators, [256,512) the A ring
+constexpr int STAGES = 4;            // A ring in tensor memory (4 x 64 columns)
+// B in shared memory: a deep ring of landed (raw, later hi) tiles so that the bulk copies run several
+// k-blocks ahead of their use, and a short ring of lo tiles filled just in time (it shares its
+// stage index and its "empty" barrier with the A ring).  Sized to what 227 KB leave next to the sums.
+constexpr int raw_stages(int bn) { return bn >= 128 ? 6 : 8; }
+constexpr int RAW_STAGES_MAX = 8;
+constexpr int A_COL_BASE = 256;      // tensor-memory columns [0,256): two partial accumulators, [256,512): the A ring
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_LOADER_WARPS = 8;  // 4 lane quadrants x 2 alternating stage groups
-constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EPI0 = 2, WARP_LOAD0 = 6;
+constexpr int CHUNK_KB = 8;          // k-blocks summed inside the tensor core before the sum moves to fp32 adds
+// Warp roles.  Tensor-memory lanes are tied to (warp index mod 4), so the accumulate and the loader
+// warps start at multiples of four (warps 2 and 3 have no role).
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_ACC0 = 4, WARP_LOAD0 = 8;
+constexpr int NUM_ACC_WARPS = 4, NUM_LOADER_WARPS = 8;
 constexpr int NUM_WARPS = WARP_LOAD0 + NUM_LOADER_WARPS;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr long long WAIT_LIMIT_NS = 400ll * 1000 * 1000;
 
 // codes left in the device status word
 enum { ST_TMA_EMPTY = 101, ST_MMA_FULL_B = 102, ST_MMA_FULL_A = 103, ST_MMA_ACC = 104, ST_EPI_ACC = 105, ST_LOAD_EMPTY = 106,
-       ST_DRAIN = 107 };
+       ST_DRAIN = 107, ST_SPLIT_RAW = 108 };
+
+// diagnostic switches (environment variable DLP_TC_DIAG, for timing experiments; results are wrong with any set)
+enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4 };
 
 struct Shared {
-    unsigned long long full_b[STAGES];
-    unsigned long long full_a[STAGES];
-    unsigned long long empty[STAGES];
-    unsigned long long acc_full[2];
-    unsigned long long acc_empty[2];
+    unsigned long long full_raw[RAW_STAGES_MAX];  // bulk copy of a B tile landed
+    unsigned long long empty_raw[RAW_STAGES_MAX]; // the MMAs that read the (hi) tile retired
+    unsigned long long full[STAGES];           // A columns written and B tile split (the 4 loader warps of the k-block's group)
+    unsigned long long empty_a[STAGES];        // the MMAs that read the A columns and the lo tile retired
+    unsigned long long acc_full[2];            // a chunk's partial sum is complete in tensor memory
+    unsigned long long acc_empty[2];           // ... and has been read out (4 accumulate warps)
     unsigned long long drain;
     uint32_t tmem_base;
     int abort_flag;
@@ -87,13 +105,18 @@ __device__ __forceinline__ long long global_ns()
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait.  Returns false when the CTA is aborting or the time limit ran out (then it raises the abort).
-__device__ __noinline__ bool mbar_wait_slow(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code)
+// Bounded wait by one thread.  Returns false when the CTA is aborting or the time limit ran out
+// (then it raises the abort).
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code)
 {
-    long long t0 = global_ns();
+    #pragma unroll 1
+    for(int i = 0; i < 32; i++)
+        if(mbar_try_wait(bar, parity)) return true;
+    const long long t0 = global_ns();
+    #pragma unroll 1
     for(uint32_t i = 0;; i++) {
         if(mbar_try_wait(bar, parity)) return true;
-        __nanosleep(64);
+        __nanosleep(32);
         if((i & 63) == 63) {
             if(*(volatile int *)&sh->abort_flag) return false;
             if(global_ns() - t0 > WAIT_LIMIT_NS) {
@@ -104,12 +127,15 @@ __device__ __noinline__ bool mbar_wait_slow(unsigned long long *bar, uint32_t pa
         }
     }
 }
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code)
+// The same for a whole warp: one lane polls (32 lanes polling one barrier serialise), all get the answer.
+__device__ __forceinline__ bool warp_wait(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code, int lane)
 {
-    #pragma unroll 1
-    for(int i = 0; i < 16; i++)
-        if(mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, sh, status, code);
+    int ok = 1;
+    __syncwarp();
+    if(lane == 0) ok = mbar_wait(bar, parity, sh, status, code) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    return ok != 0;
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -146,6 +172,42 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
                  "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The twelve MMAs of one k-block (four K=8 steps x three products), small terms first.  d, a: tensor
+// memory addresses (a_hi at a, a_lo at a+32); bhi, blo: low words of the hi / lo tile descriptors
+// (each K=8 step is 32 bytes further, +2 in descriptor units); dhi: the descriptors' common high word.
+__device__ __forceinline__ void mma_kblock(uint32_t d, uint32_t a, uint32_t bhi, uint32_t blo, uint32_t dhi, uint32_t idesc,
+                                           uint32_t accumulate_first)
+{
+    asm volatile("{\n\t"
+                 ".reg .pred p, t;\n\t"
+                 ".reg .b32 ah, al, h, l;\n\t"
+                 ".reg .b64 dh, dl;\n\t"
+                 "setp.ne.b32 p, %6, 0;\n\t"
+                 "setp.eq.b32 t, 0, 0;\n\t"
+                 "add.u32 al, %1, 32;\n\t"
+                 "mov.b64 dh, {%2, %4};\n\t"
+                 "mov.b64 dl, {%3, %4};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al], dh, %5, p;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], dl, %5, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], dh, %5, t;\n\t"
+                 "add.u32 ah, %1, 8;\n\t add.u32 al, %1, 40;\n\t add.u32 h, %2, 2;\n\t add.u32 l, %3, 2;\n\t"
+                 "mov.b64 dh, {h, %4};\n\t mov.b64 dl, {l, %4};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al], dh, %5, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dl, %5, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dh, %5, t;\n\t"
+                 "add.u32 ah, %1, 16;\n\t add.u32 al, %1, 48;\n\t add.u32 h, %2, 4;\n\t add.u32 l, %3, 4;\n\t"
+                 "mov.b64 dh, {h, %4};\n\t mov.b64 dl, {l, %4};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al], dh, %5, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dl, %5, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dh, %5, t;\n\t"
+                 "add.u32 ah, %1, 24;\n\t add.u32 al, %1, 56;\n\t add.u32 h, %2, 6;\n\t add.u32 l, %3, 6;\n\t"
+                 "mov.b64 dh, {h, %4};\n\t mov.b64 dl, {l, %4};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al], dh, %5, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dl, %5, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dh, %5, t;\n\t"
+                 "}"
+                 ::"r"(d), "r"(a), "r"(bhi), "r"(blo), "r"(dhi), "r"(idesc), "r"(accumulate_first) : "memory");
+}
 __device__ __forceinline__ void mma_commit(unsigned long long *bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -157,15 +219,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
                  ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
                  "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
 {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                   "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                   "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                  : "r"(taddr) : "memory");
 }
 
@@ -174,14 +233,14 @@ __device__ __forceinline__ float2 act_clamp(int act)
 {
     return make_float2(act == DLP_ACT_IDENTITY ? -INFINITY : 0.0f, act == DLP_ACT_RELU6 ? 6.0f : INFINITY);
 }
-// Lean store of 32 accumulator columns of one row: y = clamp(acc + bias) [then clamp(y + s*residual)].
-template<bool BIAS, bool RES>
-__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], float *y0, const float *r0, long long cs, const float *b0,
-                                            float2 clamp, float res_scale, float2 post_clamp)
+// Lean store of N output columns of one row: y = clamp(acc + bias) [then clamp(y + s*residual)].
+template<int N, bool BIAS, bool RES>
+__device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const float *r0, long long cs, const float *b0,
+                                           float2 clamp, float res_scale, float2 post_clamp)
 {
     #pragma unroll
-    for(int j = 0; j < 32; j++) {
-        float a = __uint_as_float(v[j]);
+    for(int j = 0; j < N; j++) {
+        float a = v[j];
         if(BIAS) a += __ldg(b0 + j);
         a = fminf(fmaxf(a, clamp.x), clamp.y);
         if(RES) {
@@ -201,27 +260,35 @@ struct Cursor {
 
 template<int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contraction p, int n_pad, int kblocks, int n_tiles,
-                          long long num_tiles, int *status, int dbg)
+contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contraction p, int kblocks, int n_tiles,
+                          long long num_tiles, int *status, int diag, long long *trace)
 {
+    // optional timeline of CTA 0: trace[k-block or chunk][slot] = SM clock at a few points of each role
+#define TC_TRACE(slot, idx) do { if(trace && blockIdx.x == 0 && (idx) < 64) trace[(idx) * 16 + (slot)] = clock64(); } while(0)
     extern __shared__ unsigned char smem_raw[];
-    // B ring first, 1024-byte aligned as the 128B swizzle requires; barriers after it.
+    // B ring first, 1024-byte aligned as the 128B swizzle requires; then the fp32 sums, then the barriers.
     unsigned char *smem = (unsigned char *)((uintptr_t(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr int B_TILE_BYTES = BN * BK * 4;          // one hi or lo tile
-    constexpr int STAGE_BYTES = 2 * B_TILE_BYTES;
-    Shared *sh = (Shared *)(smem + STAGES * STAGE_BYTES);
+    constexpr int B_TILE_BYTES = BN * BK * 4;          // one tile: BN rows of 128 bytes
+    constexpr int SB = raw_stages(BN);
+    unsigned char *raw_ring = smem;                                     // SB tiles as landed by TMA (read as the hi operand)
+    unsigned char *lo_ring = smem + SB * B_TILE_BYTES;                  // STAGES tiles
+    float *sums = reinterpret_cast<float *>(lo_ring + STAGES * B_TILE_BYTES);   // [BN][BM]: column-major, a thread owns a row
+    Shared *sh = (Shared *)(lo_ring + STAGES * B_TILE_BYTES + BN * BM * 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if(threadIdx.x == 0) {
+        for(int s = 0; s < SB; s++) {
+            mbar_init(&sh->full_raw[s], 1);
+            mbar_init(&sh->empty_raw[s], 1);
+        }
         for(int s = 0; s < STAGES; s++) {
-            mbar_init(&sh->full_b[s], 1);
-            mbar_init(&sh->full_a[s], 4);
-            mbar_init(&sh->empty[s], 1);
+            mbar_init(&sh->full[s], 4);
+            mbar_init(&sh->empty_a[s], 1);
         }
         for(int a = 0; a < 2; a++) {
             mbar_init(&sh->acc_full[a], 1);
-            mbar_init(&sh->acc_empty[a], 4);
+            mbar_init(&sh->acc_empty[a], NUM_ACC_WARPS);
         }
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
@@ -246,12 +313,11 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
                 const int n0 = int(tile % n_tiles) * BN;
                 for(int kb = 0; kb < kblocks; kb++, it++) {
-                    const int s = it % STAGES;
-                    if(!mbar_wait(&sh->empty[s], ((it / STAGES) & 1) ^ 1, sh, status, ST_TMA_EMPTY)) { live = false; break; }
-                    mbar_arrive_expect_tx(&sh->full_b[s], STAGE_BYTES);
-                    unsigned char *dst = smem + s * STAGE_BYTES;
-                    tma_load_2d(dst, &b_map, kb * BK, n0, &sh->full_b[s]);
-                    tma_load_2d(dst + B_TILE_BYTES, &b_map, kb * BK, n_pad + n0, &sh->full_b[s]);
+                    const int s = it % SB;
+                    if(!mbar_wait(&sh->empty_raw[s], ((it / SB) & 1) ^ 1, sh, status, ST_TMA_EMPTY)) { live = false; break; }
+                    TC_TRACE(0, it);
+                    mbar_arrive_expect_tx(&sh->full_raw[s], B_TILE_BYTES);
+                    tma_load_2d(raw_ring + s * B_TILE_BYTES, &b_map, kb * BK, n0, &sh->full_raw[s]);
                     *(volatile uint32_t *)&sh->tma_issued = it + 1;
                 }
             }
@@ -259,95 +325,119 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
     }
     else if(warp == WARP_MMA) {
         // ------------------------------------------------------------------ MMA issuer
+        // One thread feeds the tensor core.  Its instruction stream is a dependent scalar chain, so it is
+        // kept short: ring positions and barrier parities are carried incrementally, the two operand
+        // waits are one barrier (loaders and splitters arrive on the same one), and the twelve MMAs of a
+        // k-block go out as one block of PTX that derives every descriptor from two 32-bit bases.
         if(lane == 0) {
             constexpr uint32_t idesc = instr_desc_tf32(BN);
-            uint32_t it = 0, tile_iter = 0;
+            constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO, version 1, SWIZZLE_128B
+            const uint32_t raw_base = ((smem_u32(raw_ring) & 0x3FFFF) >> 4) | (1u << 16);
+            const uint32_t lo_base = ((smem_u32(lo_ring) & 0x3FFFF) >> 4) | (1u << 16);
+            uint32_t it = 0, chunk = 0;
+            uint32_t s = 0, s_phase = 0, sb = 0;          // A / lo ring position and parity, raw ring position
             bool live = true;
-            for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x, tile_iter++) {
-                const uint32_t acc = tile_iter & 1;
-                if(!mbar_wait(&sh->acc_empty[acc], ((tile_iter >> 1) & 1) ^ 1, sh, status, ST_MMA_ACC)) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
+            for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
+                int in_chunk = 0;
                 for(int kb = 0; kb < kblocks; kb++, it++) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if(!mbar_wait(&sh->full_b[s], ph, sh, status, ST_MMA_FULL_B)) { live = false; break; }
-                    *(volatile uint32_t *)&sh->mma_consumed = it + 1;
-                    if(!mbar_wait(&sh->full_a[s], ph, sh, status, ST_MMA_FULL_A)) { live = false; break; }
-                    tc_fence_after();
-                    const uint32_t b_hi = smem_u32(smem + s * STAGE_BYTES);
-                    const uint32_t b_lo = b_hi + B_TILE_BYTES;
-                    const uint32_t a_hi = tmem_base + A_COL_BASE + s * 64;
-                    const uint32_t a_lo = a_hi + 32;
-                    #pragma unroll
-                    for(int j = 0; j < BK / 8; j++) {
-                        const uint64_t dhi = smem_desc_k128(b_hi + j * 32), dlo = smem_desc_k128(b_lo + j * 32);
-                        // small terms first, the dominant product last
-                        if(dbg & 4) continue;
-                        mma_tf32_ts(d_tmem, a_lo + j * 8, dhi, idesc, (kb | j) != 0);
-                        mma_tf32_ts(d_tmem, a_hi + j * 8, dlo, idesc, 1);
-                        mma_tf32_ts(d_tmem, a_hi + j * 8, dhi, idesc, 1);
+                    const uint32_t buf = chunk & 1;
+                    if(in_chunk == 0) {
+                        // a fresh partial accumulator: the buffer must have been read out
+                        if(!mbar_wait(&sh->acc_empty[buf], ((chunk >> 1) & 1) ^ 1, sh, status, ST_MMA_ACC)) { live = false; break; }
                     }
-                    mma_commit(&sh->empty[s]);   // frees the B stage and the A columns once these MMAs retire
+                    if(!mbar_wait(&sh->full[s], s_phase, sh, status, ST_MMA_FULL_A)) { live = false; break; }
+                    tc_fence_after();
+                    TC_TRACE(2, it);
+                    if(!(diag & DIAG_NO_MMA))
+                        mma_kblock(tmem_base + buf * BN, tmem_base + A_COL_BASE + s * 64, raw_base + sb * (B_TILE_BYTES >> 4),
+                                   lo_base + s * (B_TILE_BYTES >> 4), DESC_HI, idesc, in_chunk != 0);
+                    mma_commit(&sh->empty_a[s]);   // frees the A columns, the lo tile and the raw stage once these MMAs retire
+                    mma_commit(&sh->empty_raw[sb]);
+                    TC_TRACE(3, it);
+                    if(++in_chunk == CHUNK_KB || kb == kblocks - 1) {
+                        mma_commit(&sh->acc_full[buf]);
+                        chunk++;
+                        in_chunk = 0;
+                    }
+                    if(++s == STAGES) { s = 0; s_phase ^= 1; }
+                    if(++sb == SB) sb = 0;
                 }
-                if(live) mma_commit(&sh->acc_full[acc]);
             }
+            *(volatile uint32_t *)&sh->mma_consumed = it;
         }
     }
-    else if(warp >= WARP_EPI0 && warp < WARP_LOAD0) {
-        // ------------------------------------------------------------------ epilogue
-        const int quad = warp & 3;                     // tensor-memory lanes this warp may touch
-        uint32_t tile_iter = 0;
+    else if(warp < WARP_ACC0) {
+        // warps 2 and 3: no role
+    }
+    else if(warp < WARP_LOAD0) {
+        // ------------------------------------------------------------------ accumulate + epilogue
+        const int quad = warp & 3;                          // tensor-memory lanes this warp may touch
+        const int row_in_tile = quad * 32 + lane;
+        float *my_sums = sums + row_in_tile;                // element (col) at my_sums[col * BM]: conflict-free
+        const int chunks_per_tile = (kblocks + CHUNK_KB - 1) / CHUNK_KB;
+        uint32_t chunk = 0;
         // identity / relu / relu6 are a clamp; with no per-row bias and no beta the whole epilogue is
         // add, clamp, (residual, clamp,) store.  Anything else takes the general path.
         const float2 clamp = act_clamp(p.act), post_clamp = act_clamp(p.post_act);
         const bool epi_fast = act_is_clamp(p.act) && act_is_clamp(p.post_act) && p.bias_mode != DLP_GEMM_BIAS_M && p.beta == 0.0f;
-        for(long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, tile_iter++) {
-            const uint32_t acc = tile_iter & 1;
-            const long long m_tile = tile / n_tiles;
+        bool live = true;
+        for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
             const int n0 = int(tile % n_tiles) * BN;
-            const long long row = m_tile * BM + quad * 32 + lane;
+            const long long row = (tile / n_tiles) * BM + row_in_tile;
             const RowInfo r = make_row(p, row);
-            __syncwarp();
-            if(!__all_sync(0xffffffffu, mbar_wait(&sh->acc_full[acc], (tile_iter >> 1) & 1, sh, status, ST_EPI_ACC))) break;
-            tc_fence_after();
-            // Everything that does not depend on the column is hoisted out of the store loop: the
-            // epilogue has to drain 128 x BN values per tile with only four warps.
             const long long col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : 1ll;
-            float *y_row = p.y + r.out + (long long)n0 * col_stride;
-            const float *res_row = p.residual ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
-            #pragma unroll 1
-            for(int c = 0; c < BN / 32; c++) {
-                uint32_t v[32];
-                __syncwarp();
-                tmem_ld32(tmem_base + (uint32_t(quad * 32) << 16) + acc * BN + c * 32, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if(c == BN / 32 - 1) {
-                    // accumulator fully read: hand it back before the global stores
-                    tc_fence_before();
+            for(int c = 0; c < chunks_per_tile; c++, chunk++) {
+                const uint32_t buf = chunk & 1;
+                const bool first = c == 0, last = c == chunks_per_tile - 1;
+                if(quad == 0 && lane == 0) TC_TRACE(9, chunk);
+                if(!warp_wait(&sh->acc_full[buf], (chunk >> 1) & 1, sh, status, ST_EPI_ACC, lane)) { live = false; break; }
+                if(quad == 0 && lane == 0) TC_TRACE(10, chunk);
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + buf * BN;
+                #pragma unroll 1
+                for(int part = 0; part < BN / 16; part++) {
+                    uint32_t v[16];
                     __syncwarp();
-                    if(lane == 0) mbar_arrive(&sh->acc_empty[acc]);
-                }
-                const int col0 = n0 + c * 32;
-                const int ncols = p.cols - col0;           // columns of this chunk inside the matrix
-                if(!r.valid || ncols <= 0 || (dbg & 2)) continue;
-                float *y0 = y_row + (long long)(c * 32) * col_stride;
-                if(epi_fast && ncols >= 32) {
-                    const float *b0 = p.bias + col0;
-                    if(res_row) {
-                        const float *r0 = res_row + (long long)(c * 32) * col_stride;
-                        if(p.bias_mode == DLP_GEMM_BIAS_N) store_chunk<true, true>(v, y0, r0, col_stride, b0, clamp, p.residual_scale, post_clamp);
-                        else store_chunk<false, true>(v, y0, r0, col_stride, b0, clamp, p.residual_scale, post_clamp);
+                    tmem_ld16(taddr + part * 16, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if(part == BN / 16 - 1) {
+                        // the partial accumulator is fully read: hand it back to the MMA issuer
+                        tc_fence_before();
+                        __syncwarp();
+                        if(lane == 0) mbar_arrive(&sh->acc_empty[buf]);
+                        if(quad == 0 && lane == 0) TC_TRACE(11, chunk);
+                    }
+                    float x[16];
+                    float *s16 = my_sums + part * 16 * BM;
+                    #pragma unroll
+                    for(int j = 0; j < 16; j++) x[j] = first ? __uint_as_float(v[j]) : s16[j * BM] + __uint_as_float(v[j]);
+                    if(!last) {
+                        #pragma unroll
+                        for(int j = 0; j < 16; j++) s16[j * BM] = x[j];
+                        continue;
+                    }
+                    // ---- last chunk: these 16 columns of the row are final
+                    const int col0 = n0 + part * 16;
+                    const int ncols = p.cols - col0;
+                    if(!r.valid || ncols <= 0 || (diag & DIAG_NO_STORES)) continue;
+                    float *y0 = p.y + r.out + (long long)col0 * col_stride;
+                    if(epi_fast && ncols >= 16) {
+                        const float *b0 = p.bias + col0;
+                        if(p.residual) {
+                            const float *r0 = p.residual + r.out + (long long)col0 * col_stride;
+                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<16, true, true>(x, y0, r0, col_stride, b0, clamp, p.residual_scale, post_clamp);
+                            else store_cols<16, false, true>(x, y0, r0, col_stride, b0, clamp, p.residual_scale, post_clamp);
+                        }
+                        else {
+                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<16, true, false>(x, y0, nullptr, col_stride, b0, clamp, 0.0f, post_clamp);
+                            else store_cols<16, false, false>(x, y0, nullptr, col_stride, b0, clamp, 0.0f, post_clamp);
+                        }
                     }
                     else {
-                        if(p.bias_mode == DLP_GEMM_BIAS_N) store_chunk<true, false>(v, y0, nullptr, col_stride, b0, clamp, 0.0f, post_clamp);
-                        else store_chunk<false, false>(v, y0, nullptr, col_stride, b0, clamp, 0.0f, post_clamp);
+                        #pragma unroll 4
+                        for(int j = 0; j < 16; j++)
+                            if(j < ncols) p.y[out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, x[j]);
                     }
-                }
-                else {
-                    #pragma unroll 4
-                    for(int j = 0; j < 32; j++)
-                        if(j < ncols) p.y[out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, __uint_as_float(v[j]));
                 }
             }
         }
@@ -367,18 +457,49 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             while(c.kb >= kblocks) { c.kb -= kblocks; c.tile += gridDim.x; }
         };
         // Issue the 32 loads of one k-block for this thread's row; nothing waits on them here.
+        // Per tile the thread works out once whether its row exists and, for a convolution, which of the
+        // kernel's taps fall inside the image for its pixel (a bit per tap), so the per-element work is
+        // a table entry, a bit test and the load.
+        unsigned long long tap_mask = 0;
         auto issue_loads = [&](const Cursor &c, float (&buf)[BK]) {
             if(c.tile != loaded_tile) {
                 loaded_tile = c.tile;
                 r = make_row(p, (c.tile / n_tiles) * BM + row_in_tile);
+                if(diag & DIAG_NO_A_LOADS) r.valid = false;
+                tap_mask = 0;
+                if(p.a_mode != A_STRIDED && r.valid)
+                    for(int t = 0; t < p.num_taps; t++) {
+                        const int d = __ldg(p.tap_dydx + t);
+                        const int iy = r.iy0 + (d >> 16), ix = r.ix0 + (d & 0xffff);
+                        if(unsigned(iy) < unsigned(p.in_h) && unsigned(ix) < unsigned(p.in_w)) tap_mask |= 1ull << t;
+                    }
             }
             const int k0 = c.kb * BK;
             if(p.a_mode == A_STRIDED) {
                 const float *src = p.a + r.base + (long long)k0 * p.a_k_stride;
-                #pragma unroll
-                for(int i = 0; i < BK; i++) {
-                    const bool ok = r.valid && (k0 + i) < p.k && !(dbg & 1);
-                    buf[i] = ok ? __ldg(src + (long long)i * p.a_k_stride) : 0.0f;
+                if(r.valid && k0 + BK <= p.k) {
+                    #pragma unroll
+                    for(int i = 0; i < BK; i++) buf[i] = __ldg(src + (long long)i * p.a_k_stride);
+                }
+                else {
+                    #pragma unroll
+                    for(int i = 0; i < BK; i++) {
+                        const bool ok = r.valid && (k0 + i) < p.k;
+                        buf[i] = ok ? __ldg(src + (long long)i * p.a_k_stride) : 0.0f;
+                    }
+                }
+            }
+            else if(p.a_mode == A_TAPBLOCK) {
+                const int cb = c.kb / p.num_taps, t = c.kb - cb * p.num_taps;
+                const int d = __ldg(p.tap_dydx + t);
+                const float *src = p.a + r.base + (long long)(cb * BK) * p.a_k_stride + (d >> 16) * p.in_w + (d & 0xffff);
+                if((tap_mask >> t) & 1ull) {
+                    #pragma unroll
+                    for(int i = 0; i < BK; i++) buf[i] = __ldg(src + (long long)i * p.a_k_stride);
+                }
+                else {
+                    #pragma unroll
+                    for(int i = 0; i < BK; i++) buf[i] = 0.0f;
                 }
             }
             else {
@@ -386,18 +507,21 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                 const int2 *tab = reinterpret_cast<const int2 *>(p.ktab + k0);
                 #pragma unroll
                 for(int i = 0; i < BK; i++) {
-                    const int2 t = __ldg(tab + i);
-                    const int iy = r.iy0 + (t.y >> 16), ix = r.ix0 + (t.y & 0xffff);
-                    const bool ok = r.valid && unsigned(iy) < unsigned(p.in_h) && unsigned(ix) < unsigned(p.in_w);
+                    const int2 t = __ldg(tab + i);          // offset, tap number (63 = padding beyond K: never valid)
+                    const bool ok = (tap_mask >> t.y) & 1ull;
                     buf[i] = ok ? __ldg(src + t.x) : 0.0f;
                 }
             }
         };
-        // Split the values and publish them as the A operand of stage (it % STAGES).
+        // Split the values and publish them as the A operand of stage (it % STAGES); then split this
+        // warp's quarter of the k-block's B tile.  The tensor core reads only the TF32 part of an fp32
+        // word (it ignores the low 13 mantissa bits), so the landed tile itself serves as "hi"; the
+        // remainder lo = v - tf32(v) is written at the same swizzled offsets of the stage's lo tile.
         auto publish = [&](const Cursor &c, const float (&buf)[BK]) -> bool {
-            const int s = c.it % STAGES;
-            __syncwarp();
-            if(!__all_sync(0xffffffffu, mbar_wait(&sh->empty[s], ((c.it / STAGES) & 1) ^ 1, sh, status, ST_LOAD_EMPTY))) return false;
+            const int s = c.it % STAGES, sb = c.it % SB;
+            if(quad == 0 && lane == 0) TC_TRACE(6, c.it);
+            if(!warp_wait(&sh->empty_a[s], ((c.it / STAGES) & 1) ^ 1, sh, status, ST_LOAD_EMPTY, lane)) return false;
+            if(quad == 0 && lane == 0) TC_TRACE(7, c.it);
             tc_fence_after();
             const uint32_t t_hi = tmem_base + (uint32_t(quad * 32) << 16) + A_COL_BASE + s * 64;
             #pragma unroll
@@ -406,17 +530,41 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                 #pragma unroll
                 for(int i = 0; i < 16; i++) {
                     const float v = buf[h * 16 + i];
-                    const uint32_t hb = __float_as_uint(v) & 0xffffe000u;
-                    hi[i] = hb;
-                    lo[i] = __float_as_uint(v - __uint_as_float(hb));
+                    hi[i] = __float_as_uint(v);      // the tensor core ignores the low 13 mantissa bits
+                    lo[i] = __float_as_uint(v - __uint_as_float(__float_as_uint(v) & 0xffffe000u));
                 }
                 tmem_st16(t_hi + h * 16, hi);
                 tmem_st16(t_hi + 32 + h * 16, lo);
             }
+            if(!warp_wait(&sh->full_raw[sb], (c.it / SB) & 1, sh, status, ST_SPLIT_RAW, lane)) return false;
+            if(quad == 0 && lane == 0) TC_TRACE(4, c.it);
+            {
+                constexpr int VEC = B_TILE_BYTES / 4 / 16 / 32;      // float4 per lane in a quarter tile
+                float4 *hi4 = reinterpret_cast<float4 *>(raw_ring + sb * B_TILE_BYTES + quad * (B_TILE_BYTES / 4));
+                float4 *lo4 = reinterpret_cast<float4 *>(lo_ring + s * B_TILE_BYTES + quad * (B_TILE_BYTES / 4));
+                float4 v[VEC];
+                #pragma unroll
+                for(int i = 0; i < VEC; i++) v[i] = hi4[i * 32 + lane];
+                #pragma unroll
+                for(int i = 0; i < VEC; i++) {
+                    float4 l;
+                    l.x = v[i].x - __uint_as_float(__float_as_uint(v[i].x) & 0xffffe000u);
+                    l.y = v[i].y - __uint_as_float(__float_as_uint(v[i].y) & 0xffffe000u);
+                    l.z = v[i].z - __uint_as_float(__float_as_uint(v[i].z) & 0xffffe000u);
+                    l.w = v[i].w - __uint_as_float(__float_as_uint(v[i].w) & 0xffffe000u);
+                    lo4[i * 32 + lane] = l;
+                }
+                if(quad == 0 && lane == 0) TC_TRACE(5, c.it);
+                // make the generic-proxy writes visible to the tensor core's (async proxy) reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            if(quad == 0 && lane == 0) TC_TRACE(14, c.it);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            if(quad == 0 && lane == 0) TC_TRACE(15, c.it);
             tc_fence_before();
             __syncwarp();
-            if(lane == 0) mbar_arrive(&sh->full_a[s]);
+            if(lane == 0) mbar_arrive(&sh->full[s]);
+            if(quad == 0 && lane == 0) TC_TRACE(8, c.it);
             return true;
         };
 
@@ -429,13 +577,17 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
         if(cur.tile < num_tiles) issue_loads(cur, buf_a);
         while(cur.tile < num_tiles) {
             Cursor nxt = cur;
+            if(quad == 0 && lane == 0) TC_TRACE(12, cur.it);
             advance(nxt, 2);
             if(nxt.tile < num_tiles) issue_loads(nxt, buf_b);
+            if(quad == 0 && lane == 0) TC_TRACE(13, cur.it);
             if(!publish(cur, buf_a)) break;
             cur = nxt;
             if(cur.tile >= num_tiles) break;
+            if(quad == 0 && lane == 0) TC_TRACE(12, cur.it);
             advance(nxt, 2);
             if(nxt.tile < num_tiles) issue_loads(nxt, buf_a);
+            if(quad == 0 && lane == 0) TC_TRACE(13, cur.it);
             if(!publish(cur, buf_b)) break;
             cur = nxt;
         }
@@ -451,7 +603,7 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             const uint32_t issued = *(volatile uint32_t *)&sh->tma_issued;
             for(uint32_t it = *(volatile uint32_t *)&sh->mma_consumed; it < issued; it++) {
                 const long long t0 = global_ns();
-                while(!mbar_try_wait(&sh->full_b[it % STAGES], (it / STAGES) & 1)) {
+                while(!mbar_try_wait(&sh->full_raw[it % SB], (it / SB) & 1)) {
                     __nanosleep(256);
                     if(global_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(status, 0, ST_DRAIN); break; }
                 }
@@ -474,18 +626,22 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
     }
 }
 
-// Pack B(col, k) into two padded K-major planes: hi (TF32-exact) then lo (the remainder).
-__global__ void prepack_hi_lo_kernel(const float *__restrict__ b, long long col_stride, long long k_stride, int cols, int k,
-                                     int n_pad, int k_pad, float *__restrict__ packed)
+// Pack B(col, k) into one zero-padded K-major plane [n_pad][k_pad]; the hi/lo split happens in the kernel.
+__global__ void prepack_kernel(const float *__restrict__ b, long long col_stride, long long k_stride, int cols, int k,
+                               int n_pad, int k_pad, int taps, float *__restrict__ packed)
 {
     const long long total = (long long)n_pad * k_pad;
     for(long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
         const int n = int(idx / k_pad), kk = int(idx - (long long)n * k_pad);
         float v = 0.0f;
-        if(n < cols && kk < k) v = __ldg(b + n * col_stride + kk * k_stride);
-        const float hi = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
-        packed[idx] = hi;
-        packed[total + idx] = v - hi;
+        int ks = kk;
+        if(taps > 0) {
+            // packed order (channel block, tap, channel in block) <- source order (channel, tap)
+            const int kb = kk / BK, i = kk % BK, cb = kb / taps, t = kb % taps;
+            ks = (cb * BK + i) * taps + t;
+        }
+        if(n < cols && kk < k) v = __ldg(b + n * col_stride + ks * k_stride);
+        packed[idx] = v;
     }
 }
 
@@ -503,13 +659,13 @@ TcPacked tc_packed_layout(int cols, int k)
 }
 
 dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
-                      float *packed, cudaStream_t stream)
+                      float *packed, int taps, cudaStream_t stream)
 {
     const long long total = (long long)L.n_pad * L.k_pad;
     const int threads = 256;
     const int blocks = int(std::min<long long>(ceil_div<long long>(total, threads), 8 * sm_count()));
-    tc::prepack_hi_lo_kernel<<<blocks, threads, 0, stream>>>(b, b_col_stride, b_k_stride, cols, k, L.n_pad, L.k_pad, packed);
-    DLP_LAUNCH_OK("prepack_hi_lo_kernel");
+    tc::prepack_kernel<<<blocks, threads, 0, stream>>>(b, b_col_stride, b_k_stride, cols, k, L.n_pad, L.k_pad, taps, packed);
+    DLP_LAUNCH_OK("prepack_kernel");
     return DLP_OK;
 }
 
@@ -533,7 +689,7 @@ EncodeTiledFn encode_tiled()
 template<int BN>
 dlp_status launch_bn(const Contraction &p, const TcPacked &L, const CUtensorMap &map, cudaStream_t stream)
 {
-    const int smem = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + int(sizeof(tc::Shared));
+    const int smem = 1024 + (tc::raw_stages(BN) + tc::STAGES) * BN * tc::BK * 4 + BN * tc::BM * 4 + int(sizeof(tc::Shared));
     static bool configured = false;   // per instantiation; the attribute is per function, set once per process
     if(!configured) {
         DLP_CUDA_OK(cudaFuncSetAttribute(tc::contraction_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -543,11 +699,29 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const CUtensorMap 
     const int n_tiles = L.n_pad / BN;
     const long long num_tiles = m_tiles * n_tiles;
     const int grid = int(std::min<long long>(num_tiles, sm_count()));
+    static const int diag = getenv("DLP_TC_DIAG") ? atoi(getenv("DLP_TC_DIAG")) : 0;
+    // DLP_TC_TRACE=<file>: dump the timeline of CTA 0 of every launch (synchronises; diagnostic use only)
+    static const char *trace_path = getenv("DLP_TC_TRACE");
+    static long long *trace = nullptr;
+    if(trace_path && !trace) DLP_CUDA_OK(cudaMalloc(&trace, 64 * 16 * sizeof(long long)));
+    if(trace) DLP_CUDA_OK(cudaMemsetAsync(trace, 0, 64 * 16 * sizeof(long long), stream));
     int *status = device_status_word();
     if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
-    tc::contraction_tf32x3_kernel<BN><<<grid, tc::NUM_THREADS, smem, stream>>>(map, p, L.n_pad, L.k_pad / tc::BK, n_tiles, num_tiles,
-                                                                              status, getenv("DLP_DBG") ? atoi(getenv("DLP_DBG")) : 0);
+    tc::contraction_tf32x3_kernel<BN><<<grid, tc::NUM_THREADS, smem, stream>>>(map, p, L.k_pad / tc::BK, n_tiles, num_tiles,
+                                                                              status, diag, trace);
     DLP_LAUNCH_OK("contraction_tf32x3_kernel");
+    if(trace) {
+        static long long host[64 * 16];
+        DLP_CUDA_OK(cudaStreamSynchronize(stream));
+        DLP_CUDA_OK(cudaMemcpy(host, trace, sizeof(host), cudaMemcpyDeviceToHost));
+        if(FILE *f = fopen(trace_path, "w")) {
+            for(int i = 0; i < 64; i++) {
+                for(int j = 0; j < 16; j++) fprintf(f, "%lld ", host[i * 16 + j] ? host[i * 16 + j] - host[0] : -1);
+                fprintf(f, "\n");
+            }
+            fclose(f);
+        }
+    }
     return DLP_OK;
 }
 } // namespace
@@ -559,7 +733,7 @@ dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const 
     if(!enc) return fail(DLP_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the CUDA driver");
     if(reinterpret_cast<uintptr_t>(packed) % 16 != 0) return fail(DLP_INVALID_ARGUMENT, "packed weights must be 16-byte aligned");
     CUtensorMap map;
-    const cuuint64_t dims[2] = { cuuint64_t(L.k_pad), cuuint64_t(2) * L.n_pad };
+    const cuuint64_t dims[2] = { cuuint64_t(L.k_pad), cuuint64_t(L.n_pad) };
     const cuuint64_t strides[1] = { cuuint64_t(L.k_pad) * sizeof(float) };
     const cuuint32_t box[2] = { cuuint32_t(tc::BK), cuuint32_t(L.bn) };
     const cuuint32_t elem[2] = { 1, 1 };

@@ -363,16 +363,19 @@ void Net::reshape_input(std::string const &name, Shape const &s)
     if(std::find(inputs_.begin(), inputs_.end(), name) == inputs_.end()) throw ValidationError("Unknown input tensor " + name);
     TensorSpecs &ts = tensor_specs_.at(name);
     ts = TensorSpecs(s, ts.dtype());
+    // a placeholder that carries the new shape until reshape() re-allocates
+    tensors_[name] = Tensor(nullptr, 0, s, ts.dtype());
+    drop_graph();
+    is_setup_ = false;
 }
 
 void Net::reshape()
 {
-    // an input tensor reshaped through the handle keeps its new shape
+    // the input tensors' handles say what the new input shapes are: either reshape_input() was
+    // called, or the caller reshaped net.input(i) itself, as with the reference
     for(std::string const &in : inputs_) {
         auto t = tensors_.find(in);
-        if(t != tensors_.end() && t->second.shape() != tensor_specs_.at(in).shape()
-           && t->second.shape().total_size() != tensor_specs_.at(in).shape().total_size())
-            tensor_specs_[in] = TensorSpecs(t->second.shape(), t->second.dtype());
+        if(t != tensors_.end()) tensor_specs_[in] = TensorSpecs(t->second.shape(), t->second.dtype());
     }
     for(Connection &c : connections_) {
         std::vector<Shape> in, out;
