@@ -1,0 +1,368 @@
+#!/usr/bin/env python
+"""Headline benchmark: ResNet-50 fp32 inference images/s on 1/2/4/8 B200 (BASELINE.json config 5).
+
+A step is one forward pass of the whole network over a global batch of 256 synthetic images, split by
+batch over the ranks (replicated weights, no communication during the pass, outputs gathered to rank 0
+with NCCL).  Rank 0 prints ONE JSON line.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]          this library on the GPU(s)
+  python bench.py --impl reference [...]                        the reference's own CPU Net on the host cores
+
+Launched under torch.distributed.run for N > 1 (one rank per GPU).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GLOBAL_BATCH = 256
+METRIC = "resnet50_fp32_inference_images_per_sec"
+WORKLOAD = "resnet50_v1.5_fp32_inference_b256_3x224x224_bn_folded"
+
+
+def measured_peaks():
+    """Driver-measured peaks; the stated fallback when the file is absent."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def shard(total, world, rank):
+    """Images [begin, end) of the global batch that belong to `rank`."""
+    base, extra = divmod(total, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, devices):
+        self.devices = set(devices)
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not f[0].isdigit() or int(f[0]) not in self.devices:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples under load: the upper half by power draw
+        cut = statistics.median(power)
+        loaded = [s for s, p in zip(sm, power) if p >= cut] or sm
+        return {"sm_mhz": statistics.median(loaded), "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm),
+                "power_w_max": max(power)}
+
+
+# ------------------------------------------------------------------------------------------------ reference arm
+def cpu_reference_run(steps, warmup, sample_images=2):
+    """The reference's own CPU Net (oracle/_ref, built from the reference sources) on a bounded sample of
+    the workload: `sample_images` images of the 256 per step.  Falls back to the C restatement."""
+    from dlprimitives_b200 import resnet50
+    from oracle import bindings as ob
+    net_json = resnet50.make_json(sample_images)
+    params = resnet50.make_params(net_json, seed=0)
+    x = resnet50.make_input(resnet50.make_json(GLOBAL_BATCH), seed=1)[:sample_images]
+    times = []
+    if ob.ref_available():
+        kind, cores = "reference", 1      # the reference has no threading of its own (internal BLAS)
+        net = ob.RefNet(net_json)
+        for name in net.param_names():
+            net.set_param(name, params[name])
+        net.set_tensor("data", x)
+        for i in range(warmup + steps):
+            net.forward()
+            if i >= warmup:
+                times.append(net.seconds)
+        out = net.get_tensor("prob")
+    else:
+        from oracle import netrun
+        kind, cores = "port", os.cpu_count() or 1
+        ob.set_threads(cores)
+        for i in range(warmup + steps):
+            res, sec = netrun.run(net_json, params, {"data": x})
+            if i >= warmup:
+                times.append(sec)
+        out = res["prob"]
+    sec = statistics.median(times)
+    return {"value": sample_images / sec, "unit": "images/s", "cores": cores, "kind": kind,
+            "sample": "%d of the %d images of one step through the full-size network, %d timed passes" % (sample_images, GLOBAL_BATCH, len(times)),
+            "seconds_per_pass": sec}, out, x, params
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
+    base, _, _, _ = cpu_reference_run(steps, warmup)
+    line = {"metric": METRIC, "value": base["value"], "unit": "images/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "ms_per_step": 1000.0 * GLOBAL_BATCH / base["value"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "impl": "reference",
+            "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "note": "CPU path timed on a bounded sample; ms_per_step extrapolated to 256 images"},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": base["value"], "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def layer_table(net_json, plan, step_ms, batch, peaks):
+    """Per-step algorithmic work and achieved rate.  FLOP = 2*N*Cout*OH*OW*(Cin/g)*KH*KW and
+    bytes = 4*(x + y + w + bias), the formulas of the reference's own tool (tools/flops.cpp:660-661)."""
+    shapes = {i["name"]: list(i["shape"]) for i in net_json["inputs"]}
+    shapes[net_json["inputs"][0]["name"]][0] = batch
+    ops = {op["name"]: op for op in net_json["operators"]}
+    info = {}
+    for op in net_json["operators"]:
+        o = op.get("options", {})
+        s = shapes[op["inputs"][0]]
+        flops, wbytes = 0, 0
+        if op["type"] == "Convolution2D":
+            k, st, pd = o["kernel"], o["stride"], o["pad"]
+            oh, ow = (s[2] + 2 * pd[0] - k[0]) // st[0] + 1, (s[3] + 2 * pd[1] - k[1]) // st[1] + 1
+            out = [s[0], o["channels_out"], oh, ow]
+            kk = (o["channels_in"] // o.get("groups", 1)) * k[0] * k[1]
+            flops = 2 * int(np.prod(out)) * kk
+            wbytes = 4 * (o["channels_out"] * kk + (o["channels_out"] if o.get("bias", True) else 0))
+        elif op["type"] == "Pooling2D":
+            k, st, pd = o["kernel"], o.get("stride", 1), o.get("pad", 0)
+            out = [s[0], s[1], (s[2] + 2 * pd - k) // st + 1, (s[3] + 2 * pd - k) // st + 1]
+        elif op["type"] == "GlobalPooling":
+            out = [s[0], s[1], 1, 1]
+        elif op["type"] == "InnerProduct":
+            out = [s[0], o["outputs"]]
+            flops = 2 * s[0] * o["inputs"] * o["outputs"]
+            wbytes = 4 * (o["inputs"] * o["outputs"] + o["outputs"])
+        else:
+            out = list(s)
+        for name in op["outputs"]:
+            shapes[name] = out
+        in_bytes = 4 * sum(int(np.prod(shapes[n])) for n in op["inputs"])
+        info[op["name"]] = {"flops": flops, "bytes": in_bytes + 4 * int(np.prod(out)) + wbytes, "out": out}
+    rows = []
+    tensor_peak = peaks["bf16_tflops_sustained"] / 2.0 / 3.0      # TF32 = bf16/2, three products per term
+    for line, ms in zip(plan, step_ms):
+        name = line.split(" ")[0]
+        i = dict(info[name])
+        fused = None
+        if "absorbs" in line:
+            fused = line.rsplit(" ", 1)[-1]
+            i["bytes"] += 4 * int(np.prod(i["out"]))             # the residual operand is read as well
+        tflops = i["flops"] / ms / 1e9 if ms > 0 else 0.0
+        gbs = i["bytes"] / ms / 1e6 if ms > 0 else 0.0
+        tensor_bound = "tf32x3" in line
+        rows.append({"step": name, "type": ops[name]["type"], "kernel": " ".join(line.split(" ")[2:4]), "fused": fused, "ms": ms,
+                     "gflop": i["flops"] / 1e9, "mbytes": i["bytes"] / 1e6, "tflops": tflops, "gbs": gbs,
+                     "bound": "tensor" if tensor_bound else "hbm",
+                     "frac": (tflops / tensor_peak) if tensor_bound else (gbs / peaks["hbm_gbs"])})
+    return rows, tensor_peak
+
+
+def run_gpu_arm(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from dlprimitives_b200 import capi, hostapi, resnet50
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    begin, end = shard(GLOBAL_BATCH, world, rank)
+    local_batch = end - begin
+    peaks = measured_peaks()
+
+    net_json = resnet50.make_json(local_batch)
+    params = resnet50.make_params(net_json, seed=0)           # every rank holds the full weights
+    x_all = resnet50.make_input(resnet50.make_json(GLOBAL_BATCH), seed=1)
+    net = hostapi.Net(net_json, device=local_rank)
+    for name, value in params.items():
+        net.set_param(name, value)
+    net.upload_params()
+    plan = net.plan()
+
+    stream = torch.cuda.Stream(device=dev)
+    x_host = torch.from_numpy(np.ascontiguousarray(x_all[begin:end])).pin_memory()
+    probs_local = torch.empty(local_batch, 1000, device=dev)
+    counts = [shard(GLOBAL_BATCH, world, r)[1] - shard(GLOBAL_BATCH, world, r)[0] for r in range(world)]
+    gathered = [torch.empty(c, 1000, device=dev) for c in counts] if rank == 0 and world > 1 else None
+    probs_host = torch.empty(GLOBAL_BATCH, 1000).pin_memory() if rank == 0 else None
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize(dev)
+
+    def step(end_to_end):
+        """One forward pass over this rank's shard; with end_to_end the shard comes from pinned host memory
+        and rank 0 reads the gathered probabilities back to the host."""
+        if end_to_end:
+            net.set_tensor("data", x_host, stream)
+        net.forward(stream)
+        net.copy_tensor_to("prob", probs_local, stream)
+        if world > 1:
+            dist.gather(probs_local, gathered, dst=0)
+        if end_to_end and rank == 0:
+            if world > 1:
+                off = 0
+                for g, c in zip(gathered, counts):
+                    probs_host[off:off + c].copy_(g, non_blocking=True)
+                    off += c
+            else:
+                probs_host.copy_(probs_local, non_blocking=True)
+
+    def timed(steps, end_to_end, sampler=None):
+        barrier()
+        if sampler:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step(end_to_end)
+        e1.record(stream)
+        barrier()
+        clocks = sampler.stop() if sampler else None
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), clocks
+
+    with torch.cuda.stream(stream):
+        net.set_tensor("data", x_host, stream)          # inputs resident in HBM before the timed region
+        launches0 = capi.launch_count()
+        net.forward(stream)                             # first pass: eager, packs the weights
+        stream.synchronize()
+        launches_first = capi.launch_count() - launches0
+        launches0 = capi.launch_count()
+        net.forward(stream)                             # second pass: recorded into the CUDA graph
+        stream.synchronize()
+        launches_per_forward = capi.launch_count() - launches0
+        for _ in range(max(args.warmup, 3)):
+            step(False)
+        sampler = ClockSampler(range(world)) if rank == 0 else None
+        ms_total, clocks = timed(args.steps, False, sampler)
+        for _ in range(2):
+            step(True)
+        ms_e2e, _ = timed(args.steps, True)
+        # per-operator pass for the roofline: operator by operator with an event pair around each
+        reps = [net.forward_timed(stream) for _ in range(5)]
+        step_ms = [statistics.median(v) for v in zip(*reps)]
+        status = capi.device_status(stream)
+        if rank == 0:
+            net.copy_tensor_to("prob", probs_local, stream)
+            stream.synchronize()
+            probs0 = probs_local.cpu().numpy()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if status != 0:
+        raise RuntimeError("a bounded device-side wait gave up during the benchmark, code %d" % status)
+
+    ms_per_step = ms_total / args.steps
+    value = GLOBAL_BATCH / (ms_per_step / 1000.0)
+    e2e_value = GLOBAL_BATCH / (ms_e2e / args.steps / 1000.0)
+    rows, tensor_peak = layer_table(net_json, plan, step_ms, local_batch, peaks)
+    tc = [r for r in rows if r["bound"] == "tensor"]
+    tc_ms, tc_flops = sum(r["ms"] for r in tc), sum(r["gflop"] for r in tc)
+    achieved = tc_flops / tc_ms if tc_ms > 0 else 0.0      # GFLOP / ms = TFLOP/s
+    roofline = {"bound": "tensor", "kernel": "contraction_tf32x3_kernel", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+                "frac": achieved / tensor_peak, "traffic": None, "launches": len(tc), "avg_launch_ms": tc_ms / max(len(tc), 1),
+                "peak_source": "%s bf16 sustained %.1f TFLOP/s / 2 (TF32) / 3 (products per term)" % (peaks["source"], peaks["bf16_tflops_sustained"]),
+                "share_of_forward": tc_ms / sum(r["ms"] for r in rows)}
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu, ref_out, _, _ = cpu_reference_run(2, 1)
+        err = float(np.abs(probs0[:ref_out.shape[0]] - ref_out).max())
+        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        cpu["max_abs_prob_diff_vs_gpu"] = err
+
+    out_dir = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(out_dir):
+        with open(os.path.join(out_dir, "bench_layers_n%d.json" % world), "w") as f:
+            json.dump({"local_batch": local_batch, "tensor_peak_tflops": tensor_peak, "hbm_peak_gbs": peaks["hbm_gbs"], "rows": rows}, f, indent=1)
+
+    line = {"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": local_batch, "parallelism": "batch-split x%d, replicated weights, NCCL gather of outputs" % world,
+                       "math": "3xTF32 tensor cores, fp32 accumulate", "l2": "working set per step (activations > 1 GB, input %d MB) exceeds the 126 MB L2" % (x_host.numel() * 4 // 2**20),
+                       "tflops": value * resnet50.flops_per_image(net_json) / 1e12},
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": GLOBAL_BATCH * 3 * 224 * 224 * 4, "d2h_bytes_per_step": GLOBAL_BATCH * 1000 * 4},
+            "gpu_launches": launches_per_forward * args.steps,
+            "launches_per_forward": launches_per_forward,
+            "clocks": clocks, "roofline": roofline}
+    if cpu:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if world != args.gpus:
+        raise SystemExit("--gpus %d needs %d ranks (launch with torch.distributed.run --nproc-per-node %d), got WORLD_SIZE=%d"
+                         % (args.gpus, args.gpus, args.gpus, world))
+    run_gpu_arm(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -6,6 +6,7 @@
 #include <dlprim/ops/conv2d.hpp>
 #include <dlprim/ops/inner_product.hpp>
 
+#include <cuda_runtime.h>
 #include <cstdio>
 #include <cstring>
 #include <typeinfo>
@@ -229,6 +230,44 @@ int dlp_net_forward(dlp_net *net, void *stream, int sync)
 {
     GUARD_BEGIN
     net->net.forward(ExecutionContext(static_cast<cudaStream_t>(stream)), sync != 0);
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_forward_timed(dlp_net *net, void *stream, float *step_ms, int capacity)
+{
+    GUARD_BEGIN
+    ExecutionContext e(static_cast<cudaStream_t>(stream));
+    std::shared_ptr<TimingData> timing(new TimingData());
+    e.enable_timing(timing);
+    net->net.forward(e, true);
+    timing->resolve();
+    int n = 0;
+    for(auto const &sec : timing->sections()) {
+        if(sec.parent != -1) continue;
+        if(n >= capacity) throw ValidationError("step_ms is too small");
+        step_ms[n++] = float(sec.time_ms);
+    }
+    if(n != int(net->plan.size())) throw ValidationError("timed sections do not match the plan");
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_copy_tensor_to_device(dlp_net *net, const char *name, void *dst, size_t count, void *stream)
+{
+    GUARD_BEGIN
+    Tensor &t = net->net.tensor(name);
+    if(t.shape().total_size() != count) throw ValidationError(std::string("size mismatch for tensor ") + name);
+    if(cudaMemcpyAsync(dst, t.device_ptr(), t.memory_size(), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)) != cudaSuccess)
+        throw DeviceError("cudaMemcpyAsync device to device failed");
+    return 0;
+    GUARD_END(1)
+}
+int dlp_net_copy_tensor_from_device(dlp_net *net, const char *name, const void *src, size_t count, void *stream)
+{
+    GUARD_BEGIN
+    Tensor &t = net->net.tensor(name);
+    if(t.shape().total_size() != count) throw ValidationError(std::string("size mismatch for tensor ") + name);
+    if(cudaMemcpyAsync(t.device_ptr(), src, t.memory_size(), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)) != cudaSuccess)
+        throw DeviceError("cudaMemcpyAsync device to device failed");
     return 0;
     GUARD_END(1)
 }

@@ -40,6 +40,9 @@ SYMBOLS = {
     "dlp_net_reshape_input": (_i, [_vp, C.c_char_p, _i, _ip]),
     "dlp_net_reshape": (_i, [_vp]),
     "dlp_net_forward": (_i, [_vp, _vp, _i]),
+    "dlp_net_forward_timed": (_i, [_vp, _vp, C.POINTER(C.c_float), _i]),
+    "dlp_net_copy_tensor_to_device": (_i, [_vp, C.c_char_p, _vp, _sz, _vp]),
+    "dlp_net_copy_tensor_from_device": (_i, [_vp, C.c_char_p, _vp, _sz, _vp]),
     "dlp_net_num_steps": (_i, [_vp]),
     "dlp_net_step_description": (_i, [_vp, _i, C.c_char_p, _i]),
     "dlp_net_activation_bytes": (_sz, [_vp, _i]),
@@ -211,6 +214,22 @@ class Net:
 
     def forward(self, stream=None, sync=False):
         if lib().dlp_net_forward(self.h, _stream(stream), int(sync)) != 0:
+            _fail()
+
+    def forward_timed(self, stream=None):
+        """One eager pass with an event pair around every plan step; returns milliseconds per step."""
+        n = lib().dlp_net_num_steps(self.h)
+        buf = (C.c_float * n)()
+        if lib().dlp_net_forward_timed(self.h, _stream(stream), buf, n) != 0:
+            _fail()
+        return list(buf)
+
+    def copy_tensor_to(self, name, device_tensor, stream=None):
+        if lib().dlp_net_copy_tensor_to_device(self.h, name.encode(), capi._ptr(device_tensor), device_tensor.numel(), _stream(stream)) != 0:
+            _fail()
+
+    def copy_tensor_from(self, name, device_tensor, stream=None):
+        if lib().dlp_net_copy_tensor_from_device(self.h, name.encode(), capi._ptr(device_tensor), device_tensor.numel(), _stream(stream)) != 0:
             _fail()
 
     def plan(self):

@@ -61,6 +61,13 @@ DLP_HOST_API void *dlp_net_tensor_device_ptr(dlp_net *net, const char *name);
 DLP_HOST_API int dlp_net_reshape_input(dlp_net *net, const char *name, int rank, const int *dims);
 DLP_HOST_API int dlp_net_reshape(dlp_net *net);
 DLP_HOST_API int dlp_net_forward(dlp_net *net, void *stream, int sync);
+/* One forward pass run operator by operator with a CUDA-event pair around every step of the plan
+ * (ExecutionContext timing, include/dlprim/context.hpp); step_ms receives dlp_net_num_steps() values.
+ * Synchronises the stream. */
+DLP_HOST_API int dlp_net_forward_timed(dlp_net *net, void *stream, float *step_ms, int capacity);
+/* device-to-device copies between a named tensor and caller-owned device memory, asynchronous on the stream */
+DLP_HOST_API int dlp_net_copy_tensor_to_device(dlp_net *net, const char *name, void *device_dst, size_t count, void *stream);
+DLP_HOST_API int dlp_net_copy_tensor_from_device(dlp_net *net, const char *name, const void *device_src, size_t count, void *stream);
 DLP_HOST_API int dlp_net_num_steps(const dlp_net *net);
 DLP_HOST_API int dlp_net_step_description(const dlp_net *net, int index, char *buf, int buf_size);
 DLP_HOST_API size_t dlp_net_activation_bytes(const dlp_net *net, int without_reuse);
