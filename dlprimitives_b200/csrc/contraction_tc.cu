@@ -228,6 +228,18 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
                  : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[16]) { tmem_ld16(taddr, v); }
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                   "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                   "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ bool act_is_clamp(int act) { return act == DLP_ACT_IDENTITY || act == DLP_ACT_RELU || act == DLP_ACT_RELU6; }
 __device__ __forceinline__ float2 act_clamp(int act)
 {
@@ -235,7 +247,7 @@ __device__ __forceinline__ float2 act_clamp(int act)
 }
 // Lean store of N output columns of one row: y = clamp(acc + bias) [then clamp(y + s*residual)].
 template<int N, bool BIAS, bool RES>
-__device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const float *r0, long long cs, const float *b0,
+__device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const float (&res)[N], long long cs, const float *b0,
                                            float2 clamp, float res_scale, float2 post_clamp)
 {
     #pragma unroll
@@ -244,10 +256,11 @@ __device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const
         if(BIAS) a += __ldg(b0 + j);
         a = fminf(fmaxf(a, clamp.x), clamp.y);
         if(RES) {
-            a = a + res_scale * __ldg(r0 + j * cs);
+            a = a + res_scale * res[j];
             a = fminf(fmaxf(a, post_clamp.x), post_clamp.y);
         }
-        y0[j * cs] = a;
+        *y0 = a;
+        y0 += cs;
     }
 }
 
@@ -386,6 +399,14 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             const long long row = (tile / n_tiles) * BM + row_in_tile;
             const RowInfo r = make_row(p, row);
             const long long col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : 1ll;
+            // The tile is handled 32 columns at a time: two tensor-memory loads under one wait; on the last
+            // chunk the residual operand of the same columns is fetched under that wait as well.
+            constexpr int G = BN >= 32 ? 32 : 16;
+            constexpr int GROUPS = BN / G;
+            const bool fast = epi_fast && r.valid && n0 + BN <= p.cols && !(diag & DIAG_NO_STORES);
+            const bool with_res = fast && p.residual != nullptr;
+            float *y_row = p.y + r.out + (long long)n0 * col_stride;
+            const float *res_row = with_res ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
             for(int c = 0; c < chunks_per_tile; c++, chunk++) {
                 const uint32_t buf = chunk & 1;
                 const bool first = c == 0, last = c == chunks_per_tile - 1;
@@ -395,48 +416,52 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + buf * BN;
                 #pragma unroll 1
-                for(int part = 0; part < BN / 16; part++) {
-                    uint32_t v[16];
+                for(int g = 0; g < GROUPS; g++) {
+                    uint32_t v[G];
+                    float res[G];
                     __syncwarp();
-                    tmem_ld16(taddr + part * 16, v);
+                    tmem_ld(taddr + g * G, v);
+                    if(last && with_res) {
+                        // the residual operand of these columns travels while the tensor-memory load does
+                        const float *rp = res_row + (long long)(g * G) * col_stride;
+                        #pragma unroll
+                        for(int j = 0; j < G; j++) { res[j] = __ldg(rp); rp += col_stride; }
+                    }
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if(part == BN / 16 - 1) {
+                    if(g == GROUPS - 1) {
                         // the partial accumulator is fully read: hand it back to the MMA issuer
                         tc_fence_before();
                         __syncwarp();
                         if(lane == 0) mbar_arrive(&sh->acc_empty[buf]);
                         if(quad == 0 && lane == 0) TC_TRACE(11, chunk);
                     }
-                    float x[16];
-                    float *s16 = my_sums + part * 16 * BM;
+                    float x[G];
+                    float *sg = my_sums + g * G * BM;
                     #pragma unroll
-                    for(int j = 0; j < 16; j++) x[j] = first ? __uint_as_float(v[j]) : s16[j * BM] + __uint_as_float(v[j]);
+                    for(int j = 0; j < G; j++) x[j] = first ? __uint_as_float(v[j]) : sg[j * BM] + __uint_as_float(v[j]);
                     if(!last) {
                         #pragma unroll
-                        for(int j = 0; j < 16; j++) s16[j * BM] = x[j];
+                        for(int j = 0; j < G; j++) sg[j * BM] = x[j];
                         continue;
                     }
-                    // ---- last chunk: these 16 columns of the row are final
-                    const int col0 = n0 + part * 16;
-                    const int ncols = p.cols - col0;
-                    if(!r.valid || ncols <= 0 || (diag & DIAG_NO_STORES)) continue;
-                    float *y0 = p.y + r.out + (long long)col0 * col_stride;
-                    if(epi_fast && ncols >= 16) {
+                    // ---- last chunk: these columns of the row are final
+                    const int col0 = n0 + g * G;
+                    if(fast) {
+                        float *y0 = y_row + (long long)(g * G) * col_stride;
                         const float *b0 = p.bias + col0;
-                        if(p.residual) {
-                            const float *r0 = p.residual + r.out + (long long)col0 * col_stride;
-                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<16, true, true>(x, y0, r0, col_stride, b0, clamp, p.residual_scale, post_clamp);
-                            else store_cols<16, false, true>(x, y0, r0, col_stride, b0, clamp, p.residual_scale, post_clamp);
+                        if(with_res) {
+                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp);
+                            else store_cols<G, false, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp);
                         }
                         else {
-                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<16, true, false>(x, y0, nullptr, col_stride, b0, clamp, 0.0f, post_clamp);
-                            else store_cols<16, false, false>(x, y0, nullptr, col_stride, b0, clamp, 0.0f, post_clamp);
+                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp);
+                            else store_cols<G, false, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp);
                         }
                     }
-                    else {
+                    else if(r.valid && !(diag & DIAG_NO_STORES)) {
                         #pragma unroll 4
-                        for(int j = 0; j < 16; j++)
-                            if(j < ncols) p.y[out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, x[j]);
+                        for(int j = 0; j < G; j++)
+                            if(col0 + j < p.cols) p.y[out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, x[j]);
                     }
                 }
             }
