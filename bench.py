@@ -344,6 +344,40 @@ def run_gpu_arm(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_single_conv(args):
+    """One convolution through the C ABI, repeated: the small case profiler captures are taken on.
+    --conv N,Cin,H,Cout,K,stride,pad[,groups]"""
+    import torch
+    from dlprimitives_b200 import capi
+    v = [int(t) for t in args.conv.split(",")]
+    n, cin, hw, cout, k, stride, pad = v[:7]
+    groups = v[7] if len(v) > 7 else 1
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    x = torch.randn(n, cin, hw, hw, device=dev, generator=g)
+    w = torch.randn(cout, cin // groups, k, k, device=dev, generator=g) * (2.0 / (cin // groups * k * k)) ** 0.5
+    b = torch.rand(cout, device=dev, generator=g) * 0.2 - 0.1
+    plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, stride=stride, pad=pad, groups=groups, batch=n, height=hw, width=hw,
+                              bias=True, activation="relu")
+    y = torch.empty(plan.output_shape(n), device=dev)
+    packed = plan.prepack(w)
+    for _ in range(max(args.warmup, 3)):
+        plan.enqueue_packed(x, packed, b, y)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        plan.enqueue_packed(x, packed, b, y)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 2.0 * y.numel() * (cin // groups) * k * k
+    byts = 4.0 * (x.numel() + y.numel() + w.numel() + b.numel())
+    print(json.dumps({"conv": args.conv, "algo": plan.algo(), "kernel": plan.kernel(), "ms": ms, "tflops": flops / ms / 1e9, "gbs": byts / ms / 1e6,
+                      "gflop": flops / 1e9, "mbytes": byts / 1e6, "status": capi.device_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -351,12 +385,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--conv", default=None, help="profile one convolution instead: N,Cin,H,Cout,K,stride,pad[,groups]")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.conv:
+        run_single_conv(args)
         return
     if world != args.gpus:
         raise SystemExit("--gpus %d needs %d ranks (launch with torch.distributed.run --nproc-per-node %d), got WORLD_SIZE=%d"
