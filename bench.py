@@ -211,6 +211,8 @@ def run_gpu_arm(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if GLOBAL_BATCH % world != 0:
+        raise SystemExit("the global batch of %d must divide by the number of GPUs (the gather needs equal shards)" % GLOBAL_BATCH)
     begin, end = shard(GLOBAL_BATCH, world, rank)
     local_batch = end - begin
     peaks = measured_peaks()
@@ -334,7 +336,7 @@ def run_gpu_arm(args, rank, world, local_rank):
                        "math": "3xTF32 tensor cores, fp32 accumulate", "l2": "working set per step (activations > 1 GB, input %d MB) exceeds the 126 MB L2" % (x_host.numel() * 4 // 2**20),
                        "tflops": value * resnet50.flops_per_image(net_json) / 1e12},
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": GLOBAL_BATCH * 3 * 224 * 224 * 4, "d2h_bytes_per_step": GLOBAL_BATCH * 1000 * 4},
-            "gpu_launches": launches_per_forward * args.steps,
+            "gpu_launches": launches_per_forward * args.steps * world,
             "launches_per_forward": launches_per_forward,
             "clocks": clocks, "roofline": roofline}
     if cpu:
