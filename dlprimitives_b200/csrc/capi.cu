@@ -64,37 +64,7 @@ static bool valid_act(int a) { return a >= DLP_ACT_IDENTITY && a <= DLP_ACT_RELU
 
 using namespace dlp;
 
-// ---------------------------------------------------------------------------------------------- plans
-enum ConvKernel { CK_TC, CK_FFMA, CK_DEPTHWISE };
-
-struct dlp_conv2d_plan {
-    dlp_conv2d_desc d;
-    std::string algo;        // what Conv2DBase::algo() reports
-    std::string kernel;
-    ConvKernel kind;
-    int out_h, out_w;
-    int k;                   // Cin/groups * KH * KW
-    bool strided_a;          // 1x1, stride 1, no padding: the taps are a plain stride
-    bool tapblock;           // tensor-core path with channels in blocks of 32: K runs (channel block, tap, channel)
-    TcPacked packed;
-    KTap *ktab = nullptr;    // device, k_pad entries (gather mode)
-    int *tap_dydx = nullptr; // device, one entry per kernel tap
-    int num_taps = 0;
-    int device = 0;
-};
-
-struct dlp_gemm_plan {
-    dlp_gemm_desc d;
-    bool use_tc;
-    std::string kernel;
-};
-
-struct dlp_ip_plan {
-    dlp_ip_desc d;
-    bool use_tc;
-    TcPacked packed;
-    std::string kernel;
-};
+#include "plans.cuh"
 
 static dlp_status conv_out_shape(const dlp_conv2d_desc &d, int in_h, int in_w, int *oh, int *ow)
 {

@@ -264,6 +264,9 @@ __device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const
     }
 }
 
+// timeline buffer of the DLP_TC_TRACE diagnostic (64 k-blocks x 16 slots)
+__device__ long long g_trace[64 * 16];
+
 // Position of a loader in the CTA's sequence of k-blocks (the sequence runs on across tiles).
 struct Cursor {
     long long tile;
@@ -728,7 +731,7 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const CUtensorMap 
     // DLP_TC_TRACE=<file>: dump the timeline of CTA 0 of every launch (synchronises; diagnostic use only)
     static const char *trace_path = getenv("DLP_TC_TRACE");
     static long long *trace = nullptr;
-    if(trace_path && !trace) DLP_CUDA_OK(cudaMalloc(&trace, 64 * 16 * sizeof(long long)));
+    if(trace_path && !trace) DLP_CUDA_OK(cudaGetSymbolAddress((void **)&trace, tc::g_trace));
     if(trace) DLP_CUDA_OK(cudaMemsetAsync(trace, 0, 64 * 16 * sizeof(long long), stream));
     int *status = device_status_word();
     if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
