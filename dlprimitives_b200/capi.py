@@ -79,6 +79,7 @@ SYMBOLS = {
     "dlp_ip_fwd_prepack": (_i, [_vp, _fp, _vp, _vp]),
     "dlp_ip_fwd_enqueue": (_i, [_vp, _fp, _fp, _fp, _fp, _vp, _sz, _i, _vp]),
     "dlp_ip_fwd_enqueue_packed": (_i, [_vp, _fp, _vp, _fp, _fp, _i, _vp]),
+    "dlp_ip_fwd_enqueue_static": (_i, [_vp, _fp, _fp, _fp, _fp, _i, _vp]),
     "dlp_pooling2d_output_shape": (_i, [_i, _i, _i2, _i2, _i2, _i, _ip, _ip]),
     "dlp_pooling2d_fwd": (_i, [_fp, _fp, _i, _i, _i, _i2, _i2, _i2, _i, _i, _i, _vp]),
     "dlp_global_pooling_fwd": (_i, [_fp, _fp, _i, _i, _i, _vp]),
@@ -287,6 +288,10 @@ class IPForward:
 
     def enqueue_packed(self, x, packed, bias, y, stream=None):
         check(lib().dlp_ip_fwd_enqueue_packed(self.h, _ptr(x), _ptr(packed), _ptr(bias), _ptr(y), x.shape[0], _stream(stream)))
+
+    def enqueue_static(self, x, w, bias, y, stream=None):
+        """The allocation-free variant: scratch is the library's own fixed device array (no workspace)."""
+        check(lib().dlp_ip_fwd_enqueue_static(self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(y), x.shape[0], _stream(stream)))
 
     def __del__(self):
         if getattr(self, "h", None) and _lib is not None:

@@ -179,6 +179,26 @@ DLP_API dlp_status dlp_ip_fwd_enqueue(const dlp_ip_plan *plan, const float *x, c
 DLP_API dlp_status dlp_ip_fwd_enqueue_packed(const dlp_ip_plan *plan, const float *x, const void *packed, const float *bias,
                                              float *y, int batch, void *stream);
 
+/* InnerProduct forward without any device allocation and without a caller workspace.
+ * It has no counterpart in the reference library.  It exists for callers that are not allowed to
+ * allocate device memory at the point where they need the result -- a plugin running inside another
+ * framework's memory pool, code called from an allocator callback, a harness where cudaMalloc is
+ * forbidden -- and therefore cannot hand dlp_ip_fwd_enqueue the workspace it asks for.  The scratch
+ * for the packed weights is a fixed array of DLP_IP_STATIC_SCRATCH_BYTES inside the library's device
+ * image; every GPU that loads the library holds that much memory until the process exits.
+ *   - Same arguments and result as dlp_ip_fwd_enqueue minus the workspace.
+ *   - Plans whose packed weights exceed DLP_IP_STATIC_SCRATCH_BYTES are refused with
+ *     DLP_INVALID_ARGUMENT and a message giving both sizes (a 2048 -> 1000 layer needs 8 MiB).
+ *   - The first call on each device looks up the array's device address; make that first call before
+ *     starting any stream capture.
+ *   - All calls on a device share the one array, which still holds the previous call's data when the
+ *     next one starts (each call overwrites all of it).  Two calls whose kernels may run at the same
+ *     time -- different streams without ordering, or several host threads -- race on it: order them.
+ *   - Neither this call nor anything it calls uses cudaMalloc, cudaFree or another allocating routine. */
+#define DLP_IP_STATIC_SCRATCH_BYTES (16u << 20)
+DLP_API dlp_status dlp_ip_fwd_enqueue_static(const dlp_ip_plan *plan, const float *x, const float *w, const float *bias, float *y,
+                                             int batch, void *stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Bandwidth-bound operators the inference graph needs between convolutions.
  * ---------------------------------------------------------------------------------------------- */
