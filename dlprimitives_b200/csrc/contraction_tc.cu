@@ -60,7 +60,7 @@ enum { ST_TMA_EMPTY = 101, ST_MMA_FULL_B = 102, ST_MMA_FULL_A = 103, ST_MMA_ACC 
        ST_DRAIN = 107, ST_SPLIT_RAW = 108 };
 
 // diagnostic switches (environment variable DLP_TC_DIAG, for timing experiments; results are wrong with any set)
-enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4 };
+enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4, DIAG_ONE_PRODUCT = 8 };
 
 struct Shared {
     unsigned long long full_raw[RAW_STAGES_MAX];  // bulk copy of a B tile landed
@@ -138,6 +138,15 @@ __device__ __forceinline__ bool warp_wait(unsigned long long *bar, uint32_t pari
     return ok != 0;
 }
 
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "elect.sync _|p, 0xffffffff;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -345,7 +354,9 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
         // kept short: ring positions and barrier parities are carried incrementally, the two operand
         // waits are one barrier (loaders and splitters arrive on the same one), and the twelve MMAs of a
         // k-block go out as one block of PTX that derives every descriptor from two 32-bit bases.
-        if(lane == 0) {
+        // The whole warp runs the loop with warp-uniform control flow, so the operands of the MMAs are
+        // known to be uniform; one elected lane issues the tensor-core instructions.
+        {
             constexpr uint32_t idesc = instr_desc_tf32(BN);
             constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO, version 1, SWIZZLE_128B
             const uint32_t raw_base = ((smem_u32(raw_ring) & 0x3FFFF) >> 4) | (1u << 16);
@@ -359,19 +370,27 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                     const uint32_t buf = chunk & 1;
                     if(in_chunk == 0) {
                         // a fresh partial accumulator: the buffer must have been read out
-                        if(!mbar_wait(&sh->acc_empty[buf], ((chunk >> 1) & 1) ^ 1, sh, status, ST_MMA_ACC)) { live = false; break; }
+                        if(!__all_sync(0xffffffffu, mbar_wait(&sh->acc_empty[buf], ((chunk >> 1) & 1) ^ 1, sh, status, ST_MMA_ACC))) { live = false; break; }
                     }
-                    if(!mbar_wait(&sh->full[s], s_phase, sh, status, ST_MMA_FULL_A)) { live = false; break; }
+                    if(!__all_sync(0xffffffffu, mbar_wait(&sh->full[s], s_phase, sh, status, ST_MMA_FULL_A))) { live = false; break; }
                     tc_fence_after();
-                    TC_TRACE(2, it);
-                    if(!(diag & DIAG_NO_MMA))
-                        mma_kblock(tmem_base + buf * BN, tmem_base + A_COL_BASE + s * 64, raw_base + sb * (B_TILE_BYTES >> 4),
-                                   lo_base + s * (B_TILE_BYTES >> 4), DESC_HI, idesc, in_chunk != 0);
-                    mma_commit(&sh->empty_a[s]);   // frees the A columns, the lo tile and the raw stage once these MMAs retire
-                    mma_commit(&sh->empty_raw[sb]);
-                    TC_TRACE(3, it);
+                    if(lane == 0) TC_TRACE(2, it);
+                    if(elect_one()) {
+                        if(diag & DIAG_ONE_PRODUCT) {
+                            for(int j = 0; j < 4; j++)
+                                mma_tf32_ts(tmem_base + buf * BN, tmem_base + A_COL_BASE + s * 64 + j * 8,
+                                            (uint64_t(DESC_HI) << 32) | (raw_base + sb * (B_TILE_BYTES >> 4) + 2 * j), idesc, in_chunk != 0 || j != 0);
+                        }
+                        else if(!(diag & DIAG_NO_MMA))
+                            mma_kblock(tmem_base + buf * BN, tmem_base + A_COL_BASE + s * 64, raw_base + sb * (B_TILE_BYTES >> 4),
+                                       lo_base + s * (B_TILE_BYTES >> 4), DESC_HI, idesc, in_chunk != 0);
+                        mma_commit(&sh->empty_a[s]);   // frees the A columns, the lo tile and the raw stage once these MMAs retire
+                        mma_commit(&sh->empty_raw[sb]);
+                        if(in_chunk + 1 == CHUNK_KB || kb == kblocks - 1) mma_commit(&sh->acc_full[buf]);
+                    }
+                    __syncwarp();
+                    if(lane == 0) TC_TRACE(3, it);
                     if(++in_chunk == CHUNK_KB || kb == kblocks - 1) {
-                        mma_commit(&sh->acc_full[buf]);
                         chunk++;
                         in_chunk = 0;
                     }
@@ -379,7 +398,7 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                     if(++sb == SB) sb = 0;
                 }
             }
-            *(volatile uint32_t *)&sh->mma_consumed = it;
+            if(lane == 0) *(volatile uint32_t *)&sh->mma_consumed = it;
         }
     }
     else if(warp < WARP_ACC0) {
