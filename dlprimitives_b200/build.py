@@ -28,6 +28,8 @@ CXX = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++")
 
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden", "-ccbin", CXX, "-Xptxas", "-v", "--expt-relaxed-constexpr"]
+if os.environ.get("DLP_TC_DIAGNOSTICS"):   # compile the tensor-core kernel's timeline and timing switches in
+    NVCC_FLAGS.append("-DDLP_TC_DIAGNOSTICS")
 CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-fvisibility=hidden", "-I" + os.path.join(ROOT, "include"),
              "-I" + os.path.join(CUDA_HOME, "include")]
 

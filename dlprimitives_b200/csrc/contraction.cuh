@@ -118,10 +118,14 @@ __device__ __forceinline__ float finish_output(const Contraction &p, const RowIn
 dlp_status launch_contraction_ffma(const Contraction &p, int groups, long long a_group_stride, long long b_group_stride,
                                    int out_group_channels, cudaStream_t stream);
 
-struct TcPacked {   // pre-packed B for the tensor-core kernel: [n_pad][k_pad] fp32, zero padded, K-major
-    int bn;         // column tile: 64 or 128
+// Pre-packed B for the tensor-core kernel: zero padded and already split into its TF32 part (hi) and
+// the remainder (lo).  It is a sequence of pipeline stages in the order (column tile, k-block of 32);
+// a stage is the exact shared-memory image the kernel computes from -- the hi tile (bn rows of 32
+// floats, 128-byte swizzled) followed by the lo tile -- so one contiguous bulk copy brings it in.
+struct TcPacked {
+    int bn;         // column tile: 32, 64 or 128
     int n_pad, k_pad;
-    size_t bytes() const { return size_t(n_pad) * k_pad * sizeof(float); }
+    size_t bytes() const { return size_t(2) * n_pad * k_pad * sizeof(float); }
 };
 TcPacked tc_packed_layout(int cols, int k);
 // taps > 0 packs in the A_TAPBLOCK order: packed k = ((channel block * taps + tap) * 32 + channel in block)

@@ -7,14 +7,14 @@
 // hi_a*hi_b, dropping only lo_a*lo_b (relative size 2^-22).
 //
 // Data flow per CTA (persistent, one CTA per SM, 128-row x BN-column output tiles, K in blocks of 32):
-//   * B (weights, one zero-padded K-major plane): TMA -> 128B-swizzled shared-memory ring, several
-//     k-blocks ahead of use.  The tensor core reads only the TF32 part of each fp32 word, so a landed
-//     tile is the hi operand as it is; the loader warps write the remainder to a lo tile at the same
-//     offsets just before use.  The weights therefore cross L2 once, as plain fp32.
+//   * B (weights) is split once, when it is packed: the packed operand holds, per column tile, the hi
+//     rows followed by the lo rows.  One bulk tensor copy per k-block brings both tiles into a
+//     128B-swizzled shared-memory ring, several k-blocks ahead of use.
 //   * A (activations): loader warps read the caller's NCHW tensor directly (implicit im2col, no
 //     re-layout in memory), split each value in registers and write hi/lo with tcgen05.st into a
 //     ring of tensor-memory columns.  The MMA takes A from tensor memory and B from shared memory,
-//     which keeps the shared-memory read traffic of the three products at one operand.
+//     which keeps the shared-memory read traffic of the three products at one operand.  The tensor
+//     core reads only the TF32 part of an fp32 word, so the unsplit value serves as hi.
 //   * one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8).
 //   * the tensor core adds into its fp32 accumulator with truncation, which over thousands of steps
 //     shows up as a systematic shrink of the result.  So a tensor-memory accumulator only ever holds
@@ -27,8 +27,6 @@
 // raises the CTA's abort flag, and every role then leaves its loop; the CTA drains its bulk copies
 // and frees its tensor memory before it returns.
 #include "contraction.cuh"
-#include <cuda.h>
-#include <mutex>
 #include <cstdlib>
 #include <cstdio>
 
@@ -38,12 +36,7 @@ namespace tc {
 
 constexpr int BM = 128;              // rows per tile = tensor-memory lanes
 constexpr int BK = 32;               // K per pipeline stage: 32 fp32 = one 128-byte swizzle row
-constexpr int STAGES = 4;            // A ring in tensor memory (4 x 64 columns)
-// B in shared memory: a deep ring of landed (raw, later hi) tiles so that the bulk copies run several
-// k-blocks ahead of their use, and a short ring of lo tiles filled just in time (it shares its
-// stage index and its "empty" barrier with the A ring).  Sized to what 227 KB leave next to the sums.
-constexpr int raw_stages(int bn) { return bn >= 128 ? 6 : 8; }
-constexpr int RAW_STAGES_MAX = 8;
+constexpr int STAGES = 4;            // pipeline depth: A ring in tensor memory (4 x 64 columns), B ring in shared memory
 constexpr int A_COL_BASE = 256;      // tensor-memory columns [0,256): two partial accumulators, [256,512): the A ring
 constexpr int TMEM_COLS = 512;
 constexpr int CHUNK_KB = 8;          // k-blocks summed inside the tensor core before the sum moves to fp32 adds
@@ -57,23 +50,24 @@ constexpr long long WAIT_LIMIT_NS = 400ll * 1000 * 1000;
 
 // codes left in the device status word
 enum { ST_TMA_EMPTY = 101, ST_MMA_FULL_B = 102, ST_MMA_FULL_A = 103, ST_MMA_ACC = 104, ST_EPI_ACC = 105, ST_LOAD_EMPTY = 106,
-       ST_DRAIN = 107, ST_SPLIT_RAW = 108 };
+       ST_DRAIN = 107 };
 
-// diagnostic switches (environment variable DLP_TC_DIAG, for timing experiments; results are wrong with any set)
-enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4, DIAG_ONE_PRODUCT = 8 };
+// Diagnostics are compiled in only with -DDLP_TC_DIAGNOSTICS (the hot loops are tight and share a small
+// instruction cache): the timeline (environment variable DLP_TC_TRACE=<file>) and the switches below
+// (environment variable DLP_TC_DIAG, for timing experiments; results are wrong with any set).
+enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4 };
 
 struct Shared {
-    unsigned long long full_raw[RAW_STAGES_MAX];  // bulk copy of a B tile landed
-    unsigned long long empty_raw[RAW_STAGES_MAX]; // the MMAs that read the (hi) tile retired
-    unsigned long long full[STAGES];           // A columns written and B tile split (the 4 loader warps of the k-block's group)
-    unsigned long long empty_a[STAGES];        // the MMAs that read the A columns and the lo tile retired
+    unsigned long long full_b[STAGES];         // the bulk copy of a k-block's B tiles landed
+    unsigned long long full_a[STAGES];         // its A columns are written (the 4 loader warps of the k-block's group)
+    unsigned long long empty[STAGES / 2];      // the MMAs that read a pair of stages retired: their A columns and B tiles are free
     unsigned long long acc_full[2];            // a chunk's partial sum is complete in tensor memory
     unsigned long long acc_empty[2];           // ... and has been read out (4 accumulate warps)
     unsigned long long drain;
     uint32_t tmem_base;
     int abort_flag;
     uint32_t tma_issued;     // k-blocks whose bulk copies were issued
-    uint32_t mma_consumed;   // k-blocks whose full_b barrier the MMA thread has passed
+    uint32_t mma_consumed;   // the first k-block the MMA issuer has not taken up
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -90,13 +84,25 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, u
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, uint32_t parity)
+// Barrier waits take the barrier either as a pointer or as its 32-bit shared-space address.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\t"
                  "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, uint32_t parity) { return mbar_try_wait(smem_u32(bar), parity); }
+// non-blocking: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
 __device__ __forceinline__ long long global_ns()
@@ -107,7 +113,7 @@ __device__ __forceinline__ long long global_ns()
 }
 // Bounded wait by one thread.  Returns false when the CTA is aborting or the time limit ran out
 // (then it raises the abort).
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code)
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Shared *sh, int *status, int code)
 {
     #pragma unroll 1
     for(int i = 0; i < 32; i++)
@@ -126,6 +132,15 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t pari
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Shared *sh, int *status, int code)
+{
+    if(mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, sh, status, code);
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code)
+{
+    return mbar_wait(smem_u32(bar), parity, sh, status, code);
 }
 // The same for a whole warp: one lane polls (32 lanes polling one barrier serialise), all get the answer.
 __device__ __forceinline__ bool warp_wait(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code, int lane)
@@ -150,10 +165,12 @@ __device__ __forceinline__ bool elect_one()
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, unsigned long long *bar)
+// Contiguous bulk copy global -> shared (both 16-byte aligned, size a multiple of 16); completion is
+// counted in bytes on the mbarrier.
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, unsigned long long *bar)
 {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"((unsigned long long)map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
 // Shared-memory matrix descriptor for a K-major tile with 128-byte rows and the 128B swizzle:
@@ -181,45 +198,37 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
                  "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-// The twelve MMAs of one k-block (four K=8 steps x three products), small terms first.  d, a: tensor
-// memory addresses (a_hi at a, a_lo at a+32); bhi, blo: low words of the hi / lo tile descriptors
-// (each K=8 step is 32 bytes further, +2 in descriptor units); dhi: the descriptors' common high word.
-__device__ __forceinline__ void mma_kblock(uint32_t d, uint32_t a, uint32_t bhi, uint32_t blo, uint32_t dhi, uint32_t idesc,
-                                           uint32_t accumulate_first)
+// The twelve MMAs of one k-block (four K=8 steps x three products), small terms first.  d: the
+// accumulator; ah / al: tensor-memory addresses of the hi / lo columns of A for each K=8 step;
+// bh / bl: shared-memory descriptors of the hi / lo tile of B for each step.  The operands come in
+// ready-made so that the caller can compute them in warp-uniform code.
+__device__ __forceinline__ void mma_kblock(uint32_t d, const uint32_t (&ah)[4], const uint32_t (&al)[4], const uint64_t (&bh)[4],
+                                           const uint64_t (&bl)[4], uint32_t idesc, uint32_t accumulate_first)
 {
     asm volatile("{\n\t"
                  ".reg .pred p, t;\n\t"
-                 ".reg .b32 ah, al, h, l;\n\t"
-                 ".reg .b64 dh, dl;\n\t"
-                 "setp.ne.b32 p, %6, 0;\n\t"
+                 "setp.ne.b32 p, %18, 0;\n\t"
                  "setp.eq.b32 t, 0, 0;\n\t"
-                 "add.u32 al, %1, 32;\n\t"
-                 "mov.b64 dh, {%2, %4};\n\t"
-                 "mov.b64 dl, {%3, %4};\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al], dh, %5, p;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], dl, %5, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], dh, %5, t;\n\t"
-                 "add.u32 ah, %1, 8;\n\t add.u32 al, %1, 40;\n\t add.u32 h, %2, 2;\n\t add.u32 l, %3, 2;\n\t"
-                 "mov.b64 dh, {h, %4};\n\t mov.b64 dl, {l, %4};\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al], dh, %5, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dl, %5, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dh, %5, t;\n\t"
-                 "add.u32 ah, %1, 16;\n\t add.u32 al, %1, 48;\n\t add.u32 h, %2, 4;\n\t add.u32 l, %3, 4;\n\t"
-                 "mov.b64 dh, {h, %4};\n\t mov.b64 dl, {l, %4};\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al], dh, %5, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dl, %5, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dh, %5, t;\n\t"
-                 "add.u32 ah, %1, 24;\n\t add.u32 al, %1, 56;\n\t add.u32 h, %2, 6;\n\t add.u32 l, %3, 6;\n\t"
-                 "mov.b64 dh, {h, %4};\n\t mov.b64 dl, {l, %4};\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al], dh, %5, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dl, %5, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ah], dh, %5, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%5], %9, %17, p;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %13, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %9, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%6], %10, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], %14, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], %10, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%7], %11, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%3], %15, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%3], %11, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%8], %12, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%4], %16, %17, t;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%4], %12, %17, t;\n\t"
                  "}"
-                 ::"r"(d), "r"(a), "r"(bhi), "r"(blo), "r"(dhi), "r"(idesc), "r"(accumulate_first) : "memory");
+                 ::"r"(d), "r"(ah[0]), "r"(ah[1]), "r"(ah[2]), "r"(ah[3]), "r"(al[0]), "r"(al[1]), "r"(al[2]), "r"(al[3]),
+                   "l"(bh[0]), "l"(bh[1]), "l"(bh[2]), "l"(bh[3]), "l"(bl[0]), "l"(bl[1]), "l"(bl[2]), "l"(bl[3]),
+                   "r"(idesc), "r"(accumulate_first) : "memory");
 }
-__device__ __forceinline__ void mma_commit(unsigned long long *bar)
+__device__ __forceinline__ void mma_commit(uint32_t bar)   // bar: shared-space address of the mbarrier
 {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16])
@@ -273,8 +282,10 @@ __device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const
     }
 }
 
+#ifdef DLP_TC_DIAGNOSTICS
 // timeline buffer of the DLP_TC_TRACE diagnostic (64 k-blocks x 16 slots)
 __device__ long long g_trace[64 * 16];
+#endif
 
 // Position of a loader in the CTA's sequence of k-blocks (the sequence runs on across tiles).
 struct Cursor {
@@ -283,34 +294,41 @@ struct Cursor {
     uint32_t it;
 };
 
-template<int BN>
+// BN: column tile.  MODE: how the loaders address A (A_GATHER / A_STRIDED / A_TAPBLOCK); a template
+// parameter so that each kernel carries one loader only -- the roles share a small instruction cache.
+template<int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contraction p, int kblocks, int n_tiles,
+contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p, int kblocks, int n_tiles,
                           long long num_tiles, int *status, int diag, long long *trace)
 {
+#ifdef DLP_TC_DIAGNOSTICS
     // optional timeline of CTA 0: trace[k-block or chunk][slot] = SM clock at a few points of each role
-#define TC_TRACE(slot, idx) do { if(trace && blockIdx.x == 0 && (idx) < 64) trace[(idx) * 16 + (slot)] = clock64(); } while(0)
+    // (bits 8.. of diag, when set, select which slots are recorded, so that a measurement can run with few probes)
+    const uint32_t trace_slots = trace && blockIdx.x == 0 ? ((diag >> 8) ? uint32_t(diag >> 8) : 0xffffu) : 0u;
+#define TC_TRACE(slot, idx) do { if(((trace_slots >> (slot)) & 1u) && (idx) < 64) trace[(idx) * 16 + (slot)] = clock64(); } while(0)
+#define TC_DIAG(bit) (diag & (bit))
+#else
+#define TC_TRACE(slot, idx) do { } while(0)
+#define TC_DIAG(bit) false
+#endif
     extern __shared__ unsigned char smem_raw[];
     // B ring first, 1024-byte aligned as the 128B swizzle requires; then the fp32 sums, then the barriers.
-    unsigned char *smem = (unsigned char *)((uintptr_t(smem_raw) + 1023) & ~uintptr_t(1023));
+    // (The offset is applied to the shared array itself so that accesses stay in the shared state space.)
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int B_TILE_BYTES = BN * BK * 4;          // one tile: BN rows of 128 bytes
-    constexpr int SB = raw_stages(BN);
-    unsigned char *raw_ring = smem;                                     // SB tiles as landed by TMA (read as the hi operand)
-    unsigned char *lo_ring = smem + SB * B_TILE_BYTES;                  // STAGES tiles
-    float *sums = reinterpret_cast<float *>(lo_ring + STAGES * B_TILE_BYTES);   // [BN][BM]: column-major, a thread owns a row
-    Shared *sh = (Shared *)(lo_ring + STAGES * B_TILE_BYTES + BN * BM * 4);
+    constexpr int B_STAGE_BYTES = 2 * B_TILE_BYTES;    // hi tile, then lo tile
+    unsigned char *b_ring = smem;
+    float *sums = reinterpret_cast<float *>(smem + STAGES * B_STAGE_BYTES);   // [BN][BM]: column-major, a thread owns a row
+    Shared *sh = reinterpret_cast<Shared *>(smem + STAGES * B_STAGE_BYTES + BN * BM * 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if(threadIdx.x == 0) {
-        for(int s = 0; s < SB; s++) {
-            mbar_init(&sh->full_raw[s], 1);
-            mbar_init(&sh->empty_raw[s], 1);
-        }
         for(int s = 0; s < STAGES; s++) {
-            mbar_init(&sh->full[s], 4);
-            mbar_init(&sh->empty_a[s], 1);
+            mbar_init(&sh->full_b[s], 1);
+            mbar_init(&sh->full_a[s], 4);
         }
+        for(int s = 0; s < STAGES / 2; s++) mbar_init(&sh->empty[s], 1);
         for(int a = 0; a < 2; a++) {
             mbar_init(&sh->acc_full[a], 1);
             mbar_init(&sh->acc_empty[a], NUM_ACC_WARPS);
@@ -336,13 +354,15 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             uint32_t it = 0;
             bool live = true;
             for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
-                const int n0 = int(tile % n_tiles) * BN;
+                // the packed operand holds the stages in the order (column tile, k-block), each one the exact
+                // shared-memory image of its hi and lo tiles
+                const float *src = packed + (long long)(tile % n_tiles) * kblocks * (B_STAGE_BYTES / 4);
                 for(int kb = 0; kb < kblocks; kb++, it++) {
-                    const int s = it % SB;
-                    if(!mbar_wait(&sh->empty_raw[s], ((it / SB) & 1) ^ 1, sh, status, ST_TMA_EMPTY)) { live = false; break; }
+                    const int s = it % STAGES;
+                    if(!mbar_wait(&sh->empty[s >> 1], ((it / STAGES) & 1) ^ 1, sh, status, ST_TMA_EMPTY)) { live = false; break; }
                     TC_TRACE(0, it);
-                    mbar_arrive_expect_tx(&sh->full_raw[s], B_TILE_BYTES);
-                    tma_load_2d(raw_ring + s * B_TILE_BYTES, &b_map, kb * BK, n0, &sh->full_raw[s]);
+                    mbar_arrive_expect_tx(&sh->full_b[s], B_STAGE_BYTES);
+                    bulk_load(b_ring + s * B_STAGE_BYTES, src + (long long)kb * (B_STAGE_BYTES / 4), B_STAGE_BYTES, &sh->full_b[s]);
                     *(volatile uint32_t *)&sh->tma_issued = it + 1;
                 }
             }
@@ -350,56 +370,80 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
     }
     else if(warp == WARP_MMA) {
         // ------------------------------------------------------------------ MMA issuer
-        // One thread feeds the tensor core.  Its instruction stream is a dependent scalar chain, so it is
-        // kept short: ring positions and barrier parities are carried incrementally, the two operand
-        // waits are one barrier (loaders and splitters arrive on the same one), and the twelve MMAs of a
-        // k-block go out as one block of PTX that derives every descriptor from two 32-bit bases.
-        // The whole warp runs the loop with warp-uniform control flow, so the operands of the MMAs are
-        // known to be uniform; one elected lane issues the tensor-core instructions.
-        {
-            constexpr uint32_t idesc = instr_desc_tf32(BN);
-            constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO, version 1, SWIZZLE_128B
-            const uint32_t raw_base = ((smem_u32(raw_ring) & 0x3FFFF) >> 4) | (1u << 16);
-            const uint32_t lo_base = ((smem_u32(lo_ring) & 0x3FFFF) >> 4) | (1u << 16);
-            uint32_t it = 0, chunk = 0;
-            uint32_t s = 0, s_phase = 0, sb = 0;          // A / lo ring position and parity, raw ring position
-            bool live = true;
-            for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
-                int in_chunk = 0;
-                for(int kb = 0; kb < kblocks; kb++, it++) {
-                    const uint32_t buf = chunk & 1;
-                    if(in_chunk == 0) {
-                        // a fresh partial accumulator: the buffer must have been read out
-                        if(!__all_sync(0xffffffffu, mbar_wait(&sh->acc_empty[buf], ((chunk >> 1) & 1) ^ 1, sh, status, ST_MMA_ACC))) { live = false; break; }
-                    }
-                    if(!__all_sync(0xffffffffu, mbar_wait(&sh->full[s], s_phase, sh, status, ST_MMA_FULL_A))) { live = false; break; }
-                    tc_fence_after();
-                    if(lane == 0) TC_TRACE(2, it);
-                    if(elect_one()) {
-                        if(diag & DIAG_ONE_PRODUCT) {
-                            for(int j = 0; j < 4; j++)
-                                mma_tf32_ts(tmem_base + buf * BN, tmem_base + A_COL_BASE + s * 64 + j * 8,
-                                            (uint64_t(DESC_HI) << 32) | (raw_base + sb * (B_TILE_BYTES >> 4) + 2 * j), idesc, in_chunk != 0 || j != 0);
-                        }
-                        else if(!(diag & DIAG_NO_MMA))
-                            mma_kblock(tmem_base + buf * BN, tmem_base + A_COL_BASE + s * 64, raw_base + sb * (B_TILE_BYTES >> 4),
-                                       lo_base + s * (B_TILE_BYTES >> 4), DESC_HI, idesc, in_chunk != 0);
-                        mma_commit(&sh->empty_a[s]);   // frees the A columns, the lo tile and the raw stage once these MMAs retire
-                        mma_commit(&sh->empty_raw[sb]);
-                        if(in_chunk + 1 == CHUNK_KB || kb == kblocks - 1) mma_commit(&sh->acc_full[buf]);
-                    }
-                    __syncwarp();
-                    if(lane == 0) TC_TRACE(3, it);
-                    if(++in_chunk == CHUNK_KB || kb == kblocks - 1) {
-                        chunk++;
-                        in_chunk = 0;
-                    }
-                    if(++s == STAGES) { s = 0; s_phase ^= 1; }
-                    if(++sb == SB) sb = 0;
-                }
+        // One thread feeds the tensor core, and what it executes per k-block is a dependent scalar chain
+        // that has to stay shorter than the tensor core's own time for the k-block.  So:
+        //  * the whole warp runs the loop with warp-uniform control flow and every MMA operand is computed
+        //    outside the elected region, so the operands can stay in uniform registers;
+        //  * lanes 0..2 each watch one barrier of the coming k-block (its A columns, its B tiles, and when it
+        //    opens a partial accumulator "read out"); the barriers of k-block it+1 are tested before the
+        //    MMAs of k-block it go out and the answer is collected after them, so in the steady state
+        //    the issuer never sits in a wait;
+        //  * a commit costs about as much as six MMAs, so stages are released in pairs.
+        constexpr uint32_t idesc = instr_desc_tf32(BN);
+        constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO, version 1, SWIZZLE_128B
+        const uint32_t ring_base = ((smem_u32(b_ring) & 0x3FFFF) >> 4) | (1u << 16);
+        const uint32_t acc_empty0 = smem_u32(&sh->acc_empty[0]), empty0 = smem_u32(&sh->empty[0]), acc_full0 = smem_u32(&sh->acc_full[0]);
+        // the barrier array this lane watches (8 bytes per entry): lane 0 the A columns, lane 1 the B tiles
+        const uint32_t watch_base = smem_u32(lane == 1 ? &sh->full_b[0] : &sh->full_a[0]);
+        const long long my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const uint32_t total = uint32_t(my_tiles * kblocks);
+        uint32_t chunk = 0, s = 0, s_phase = 0;           // partial accumulators so far; ring position and parity
+        int kb = 0, in_chunk = 0;
+        bool ready = false;
+        uint32_t it = 0;
+        #pragma unroll 1
+        for(; it < total; it++) {
+            const uint32_t buf = chunk & 1;
+            const bool closes_chunk = in_chunk + 1 == CHUNK_KB || kb + 1 == kblocks;
+            if(!ready) {
+                const bool mine = lane < 2 || (lane == 2 && in_chunk == 0);
+                const uint32_t bar = lane == 2 ? acc_empty0 + 8 * buf : watch_base + 8 * s;
+                const uint32_t parity = lane == 2 ? ((chunk >> 1) & 1) ^ 1 : s_phase;
+                const int code = lane == 0 ? ST_MMA_FULL_A : (lane == 1 ? ST_MMA_FULL_B : ST_MMA_ACC);
+                const bool ok = mine ? mbar_wait(bar, parity, sh, status, code) : true;
+                if(!__all_sync(0xffffffffu, ok)) break;
             }
-            if(lane == 0) *(volatile uint32_t *)&sh->mma_consumed = it;
+            if(lane == 0) TC_TRACE(2, it);
+            tc_fence_after();
+            // look ahead: the next k-block's barriers
+            bool peek = true;
+            {
+                const uint32_t ns = (s + 1) & (STAGES - 1);
+                const bool mine = lane < 2 || (lane == 2 && closes_chunk);
+                const uint32_t bar = lane == 2 ? acc_empty0 + 8 * (buf ^ 1) : watch_base + 8 * ns;
+                const uint32_t parity = lane == 2 ? (((chunk + 1) >> 1) & 1) ^ 1 : (ns == 0 ? s_phase ^ 1 : s_phase);
+                if(mine) peek = mbar_test(bar, parity);
+            }
+            const uint32_t d = tmem_base + buf * BN, a = tmem_base + A_COL_BASE + s * 64;
+            const uint32_t bhi = ring_base + s * (B_STAGE_BYTES >> 4), blo = bhi + (B_TILE_BYTES >> 4);
+            uint32_t ah[4], al[4];
+            uint64_t bh[4], bl[4];
+            #pragma unroll
+            for(int j = 0; j < 4; j++) {
+                // K=8 step j: 8 columns further in A, 32 bytes (2 descriptor units) further in the B rows
+                ah[j] = a + 8 * j;
+                al[j] = a + 32 + 8 * j;
+                bh[j] = (uint64_t(DESC_HI) << 32) | (bhi + 2 * j);
+                bl[j] = (uint64_t(DESC_HI) << 32) | (blo + 2 * j);
+            }
+            const uint32_t accumulate = in_chunk != 0;
+            if(elect_one()) {
+                TC_TRACE(6, it);
+                if(!TC_DIAG(DIAG_NO_MMA)) mma_kblock(d, ah, al, bh, bl, idesc, accumulate);
+                TC_TRACE(5, it);
+                if(s & 1) mma_commit(empty0 + 8 * (s >> 1));   // frees the A columns and the B tiles of this stage and the one before
+                if(closes_chunk) mma_commit(acc_full0 + 8 * buf);
+                TC_TRACE(3, it);
+            }
+            ready = __all_sync(0xffffffffu, peek);
+            if(lane == 0) TC_TRACE(1, it);
+            if(closes_chunk) { chunk++; in_chunk = 0; }
+            else in_chunk++;
+            if(++kb == kblocks) kb = 0;
+            s = (s + 1) & (STAGES - 1);
+            if(s == 0) s_phase ^= 1;
         }
+        if(lane == 0) *(volatile uint32_t *)&sh->mma_consumed = it;
     }
     else if(warp < WARP_ACC0) {
         // warps 2 and 3: no role
@@ -425,7 +469,7 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             // chunk the residual operand of the same columns is fetched under that wait as well.
             constexpr int G = BN >= 32 ? 32 : 16;
             constexpr int GROUPS = BN / G;
-            const bool fast = epi_fast && r.valid && n0 + BN <= p.cols && !(diag & DIAG_NO_STORES);
+            const bool fast = epi_fast && r.valid && n0 + BN <= p.cols && !TC_DIAG(DIAG_NO_STORES);
             const bool with_res = fast && p.residual != nullptr;
             float *y_row = p.y + r.out + (long long)n0 * col_stride;
             const float *res_row = with_res ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
@@ -480,10 +524,17 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                             else store_cols<G, false, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp);
                         }
                     }
-                    else if(r.valid && !(diag & DIAG_NO_STORES)) {
-                        #pragma unroll 4
-                        for(int j = 0; j < G; j++)
-                            if(col0 + j < p.cols) p.y[out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, x[j]);
+                    else {
+                        // general epilogue: the values pass through the thread's own slots of the sums tile so
+                        // that this loop can index them (a register array indexed by a loop counter would live
+                        // in local memory on every path)
+                        #pragma unroll
+                        for(int j = 0; j < G; j++) sg[j * BM] = x[j];
+                        if(r.valid && !TC_DIAG(DIAG_NO_STORES)) {
+                            #pragma unroll 1
+                            for(int j = 0; j < G; j++)
+                                if(col0 + j < p.cols) p.y[out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, sg[j * BM]);
+                        }
                     }
                 }
             }
@@ -512,9 +563,9 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             if(c.tile != loaded_tile) {
                 loaded_tile = c.tile;
                 r = make_row(p, (c.tile / n_tiles) * BM + row_in_tile);
-                if(diag & DIAG_NO_A_LOADS) r.valid = false;
+                if(TC_DIAG(DIAG_NO_A_LOADS)) r.valid = false;
                 tap_mask = 0;
-                if(p.a_mode != A_STRIDED && r.valid)
+                if(MODE != A_STRIDED && r.valid)
                     for(int t = 0; t < p.num_taps; t++) {
                         const int d = __ldg(p.tap_dydx + t);
                         const int iy = r.iy0 + (d >> 16), ix = r.ix0 + (d & 0xffff);
@@ -522,7 +573,7 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                     }
             }
             const int k0 = c.kb * BK;
-            if(p.a_mode == A_STRIDED) {
+            if(MODE == A_STRIDED) {
                 const float *src = p.a + r.base + (long long)k0 * p.a_k_stride;
                 if(r.valid && k0 + BK <= p.k) {
                     #pragma unroll
@@ -536,7 +587,7 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                     }
                 }
             }
-            else if(p.a_mode == A_TAPBLOCK) {
+            else if(MODE == A_TAPBLOCK) {
                 const int cb = c.kb / p.num_taps, t = c.kb - cb * p.num_taps;
                 const int d = __ldg(p.tap_dydx + t);
                 const float *src = p.a + r.base + (long long)(cb * BK) * p.a_k_stride + (d >> 16) * p.in_w + (d & 0xffff);
@@ -560,14 +611,13 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                 }
             }
         };
-        // Split the values and publish them as the A operand of stage (it % STAGES); then split this
-        // warp's quarter of the k-block's B tile.  The tensor core reads only the TF32 part of an fp32
-        // word (it ignores the low 13 mantissa bits), so the landed tile itself serves as "hi"; the
-        // remainder lo = v - tf32(v) is written at the same swizzled offsets of the stage's lo tile.
+        // Split the values and publish them as the A operand of stage (it % STAGES).  The tensor core reads
+        // only the TF32 part of an fp32 word (it ignores the low 13 mantissa bits), so the value itself
+        // serves as "hi"; the remainder lo = v - tf32(v) goes to the 32 columns after it.
         auto publish = [&](const Cursor &c, const float (&buf)[BK]) -> bool {
-            const int s = c.it % STAGES, sb = c.it % SB;
+            const int s = c.it % STAGES;
             if(quad == 0 && lane == 0) TC_TRACE(6, c.it);
-            if(!warp_wait(&sh->empty_a[s], ((c.it / STAGES) & 1) ^ 1, sh, status, ST_LOAD_EMPTY, lane)) return false;
+            if(!warp_wait(&sh->empty[s >> 1], ((c.it / STAGES) & 1) ^ 1, sh, status, ST_LOAD_EMPTY, lane)) return false;
             if(quad == 0 && lane == 0) TC_TRACE(7, c.it);
             tc_fence_after();
             const uint32_t t_hi = tmem_base + (uint32_t(quad * 32) << 16) + A_COL_BASE + s * 64;
@@ -577,66 +627,43 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
                 #pragma unroll
                 for(int i = 0; i < 16; i++) {
                     const float v = buf[h * 16 + i];
-                    hi[i] = __float_as_uint(v);      // the tensor core ignores the low 13 mantissa bits
+                    hi[i] = __float_as_uint(v);
                     lo[i] = __float_as_uint(v - __uint_as_float(__float_as_uint(v) & 0xffffe000u));
                 }
                 tmem_st16(t_hi + h * 16, hi);
                 tmem_st16(t_hi + 32 + h * 16, lo);
-            }
-            if(!warp_wait(&sh->full_raw[sb], (c.it / SB) & 1, sh, status, ST_SPLIT_RAW, lane)) return false;
-            if(quad == 0 && lane == 0) TC_TRACE(4, c.it);
-            {
-                constexpr int VEC = B_TILE_BYTES / 4 / 16 / 32;      // float4 per lane in a quarter tile
-                float4 *hi4 = reinterpret_cast<float4 *>(raw_ring + sb * B_TILE_BYTES + quad * (B_TILE_BYTES / 4));
-                float4 *lo4 = reinterpret_cast<float4 *>(lo_ring + s * B_TILE_BYTES + quad * (B_TILE_BYTES / 4));
-                float4 v[VEC];
-                #pragma unroll
-                for(int i = 0; i < VEC; i++) v[i] = hi4[i * 32 + lane];
-                #pragma unroll
-                for(int i = 0; i < VEC; i++) {
-                    float4 l;
-                    l.x = v[i].x - __uint_as_float(__float_as_uint(v[i].x) & 0xffffe000u);
-                    l.y = v[i].y - __uint_as_float(__float_as_uint(v[i].y) & 0xffffe000u);
-                    l.z = v[i].z - __uint_as_float(__float_as_uint(v[i].z) & 0xffffe000u);
-                    l.w = v[i].w - __uint_as_float(__float_as_uint(v[i].w) & 0xffffe000u);
-                    lo4[i * 32 + lane] = l;
-                }
-                if(quad == 0 && lane == 0) TC_TRACE(5, c.it);
-                // make the generic-proxy writes visible to the tensor core's (async proxy) reads
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             if(quad == 0 && lane == 0) TC_TRACE(14, c.it);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             if(quad == 0 && lane == 0) TC_TRACE(15, c.it);
             tc_fence_before();
             __syncwarp();
-            if(lane == 0) mbar_arrive(&sh->full[s]);
+            if(lane == 0) mbar_arrive(&sh->full_a[s]);
             if(quad == 0 && lane == 0) TC_TRACE(8, c.it);
             return true;
         };
 
-        // Two register buffers: the loads of this warp's next k-block are in flight while the
-        // current one is split and stored.
-        float buf_a[BK], buf_b[BK];
-        Cursor cur;
-        cur.tile = blockIdx.x; cur.kb = 0; cur.it = 0;
-        advance(cur, group);
-        if(cur.tile < num_tiles) issue_loads(cur, buf_a);
-        while(cur.tile < num_tiles) {
-            Cursor nxt = cur;
-            if(quad == 0 && lane == 0) TC_TRACE(12, cur.it);
-            advance(nxt, 2);
-            if(nxt.tile < num_tiles) issue_loads(nxt, buf_b);
-            if(quad == 0 && lane == 0) TC_TRACE(13, cur.it);
-            if(!publish(cur, buf_a)) break;
+        // Two register buffers: the loads of this warp's next k-block are in flight while the current one
+        // is split and stored.  The loop holds one copy of each step and hands the buffer over by moves.
+        float cur_buf[BK], nxt_buf[BK];
+        Cursor cur, nxt;
+        nxt.tile = blockIdx.x; nxt.kb = 0; nxt.it = 0;
+        advance(nxt, group);
+        cur = nxt;
+        bool have_cur = false;
+        #pragma unroll 1
+        for(;;) {
+            const bool more = nxt.tile < num_tiles;
+            if(quad == 0 && lane == 0) TC_TRACE(12, nxt.it);
+            if(more) issue_loads(nxt, nxt_buf);
+            if(quad == 0 && lane == 0) TC_TRACE(13, nxt.it);
+            if(have_cur && !publish(cur, cur_buf)) break;
+            if(!more) break;
+            #pragma unroll
+            for(int i = 0; i < BK; i++) cur_buf[i] = nxt_buf[i];
             cur = nxt;
-            if(cur.tile >= num_tiles) break;
-            if(quad == 0 && lane == 0) TC_TRACE(12, cur.it);
+            have_cur = true;
             advance(nxt, 2);
-            if(nxt.tile < num_tiles) issue_loads(nxt, buf_a);
-            if(quad == 0 && lane == 0) TC_TRACE(13, cur.it);
-            if(!publish(cur, buf_b)) break;
-            cur = nxt;
         }
     }
 
@@ -650,14 +677,14 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
             const uint32_t issued = *(volatile uint32_t *)&sh->tma_issued;
             for(uint32_t it = *(volatile uint32_t *)&sh->mma_consumed; it < issued; it++) {
                 const long long t0 = global_ns();
-                while(!mbar_try_wait(&sh->full_raw[it % SB], (it / SB) & 1)) {
+                while(!mbar_try_wait(&sh->full_b[it % STAGES], (it / STAGES) & 1)) {
                     __nanosleep(256);
                     if(global_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(status, 0, ST_DRAIN); break; }
                 }
             }
         }
-        if(warp == WARP_MMA && lane == 0) {
-            mma_commit(&sh->drain);
+        if(warp == WARP_MMA && elect_one()) {
+            mma_commit(smem_u32(&sh->drain));
             const long long t0 = global_ns();
             while(!mbar_try_wait(&sh->drain, 0)) {
                 __nanosleep(256);
@@ -673,22 +700,31 @@ contraction_tf32x3_kernel(const __grid_constant__ CUtensorMap b_map, const Contr
     }
 }
 
-// Pack B(col, k) into one zero-padded K-major plane [n_pad][k_pad]; the hi/lo split happens in the kernel.
+// Pack B(col, k): zero-padded, split into hi and lo, and laid out as the kernel's shared-memory stages
+// (see TcPacked): stage (column tile, k-block) = hi tile then lo tile, each bn rows of 32 floats with the
+// 16-byte chunks of a row permuted by the 128-byte swizzle (chunk ^ (row & 7)).
 __global__ void prepack_kernel(const float *__restrict__ b, long long col_stride, long long k_stride, int cols, int k,
-                               int n_pad, int k_pad, int taps, float *__restrict__ packed)
+                               int n_pad, int k_pad, int bn, int taps, float *__restrict__ packed)
 {
     const long long total = (long long)n_pad * k_pad;
+    const int kblocks = k_pad / BK;
     for(long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
         const int n = int(idx / k_pad), kk = int(idx - (long long)n * k_pad);
+        const int kb = kk / BK, i = kk % BK;
         float v = 0.0f;
         int ks = kk;
         if(taps > 0) {
             // packed order (channel block, tap, channel in block) <- source order (channel, tap)
-            const int kb = kk / BK, i = kk % BK, cb = kb / taps, t = kb % taps;
+            const int cb = kb / taps, t = kb % taps;
             ks = (cb * BK + i) * taps + t;
         }
         if(n < cols && kk < k) v = __ldg(b + n * col_stride + ks * k_stride);
-        packed[idx] = v;
+        const float hi = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        const int tile = n / bn, r = n % bn;
+        const long long stage = ((long long)tile * kblocks + kb) * (2 * bn * BK);
+        const int off = r * BK + (((i >> 2) ^ (r & 7)) << 2) + (i & 3);
+        packed[stage + off] = hi;
+        packed[stage + bn * BK + off] = v - hi;
     }
 }
 
@@ -711,52 +747,43 @@ dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride,
     const long long total = (long long)L.n_pad * L.k_pad;
     const int threads = 256;
     const int blocks = int(std::min<long long>(ceil_div<long long>(total, threads), 8 * sm_count()));
-    tc::prepack_kernel<<<blocks, threads, 0, stream>>>(b, b_col_stride, b_k_stride, cols, k, L.n_pad, L.k_pad, taps, packed);
+    tc::prepack_kernel<<<blocks, threads, 0, stream>>>(b, b_col_stride, b_k_stride, cols, k, L.n_pad, L.k_pad, L.bn, taps, packed);
     DLP_LAUNCH_OK("prepack_kernel");
     return DLP_OK;
 }
 
 namespace {
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled()
+template<int BN, int MODE>
+dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream)
 {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void *sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    });
-    return fn;
-}
-
-template<int BN>
-dlp_status launch_bn(const Contraction &p, const TcPacked &L, const CUtensorMap &map, cudaStream_t stream)
-{
-    const int smem = 1024 + (tc::raw_stages(BN) + tc::STAGES) * BN * tc::BK * 4 + BN * tc::BM * 4 + int(sizeof(tc::Shared));
+    const int smem = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int(sizeof(tc::Shared));
     static bool configured = false;   // per instantiation; the attribute is per function, set once per process
     if(!configured) {
-        DLP_CUDA_OK(cudaFuncSetAttribute(tc::contraction_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        DLP_CUDA_OK(cudaFuncSetAttribute(tc::contraction_tf32x3_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         configured = true;
     }
     const long long m_tiles = ceil_div<long long>(p.rows, tc::BM);
     const int n_tiles = L.n_pad / BN;
     const long long num_tiles = m_tiles * n_tiles;
     const int grid = int(std::min<long long>(num_tiles, sm_count()));
-    static const int diag = getenv("DLP_TC_DIAG") ? atoi(getenv("DLP_TC_DIAG")) : 0;
+    int diag = 0;
+    long long *trace = nullptr;
+#ifdef DLP_TC_DIAGNOSTICS
+    static const int diag_env = getenv("DLP_TC_DIAG") ? atoi(getenv("DLP_TC_DIAG")) : 0;
     // DLP_TC_TRACE=<file>: dump the timeline of CTA 0 of every launch (synchronises; diagnostic use only)
     static const char *trace_path = getenv("DLP_TC_TRACE");
-    static long long *trace = nullptr;
-    if(trace_path && !trace) DLP_CUDA_OK(cudaGetSymbolAddress((void **)&trace, tc::g_trace));
-    if(trace) DLP_CUDA_OK(cudaMemsetAsync(trace, 0, 64 * 16 * sizeof(long long), stream));
+    static long long *trace_buf = nullptr;
+    if(trace_path && !trace_buf) DLP_CUDA_OK(cudaGetSymbolAddress((void **)&trace_buf, tc::g_trace));
+    if(trace_buf) DLP_CUDA_OK(cudaMemsetAsync(trace_buf, 0, 64 * 16 * sizeof(long long), stream));
+    diag = diag_env;
+    trace = trace_buf;
+#endif
     int *status = device_status_word();
     if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
-    tc::contraction_tf32x3_kernel<BN><<<grid, tc::NUM_THREADS, smem, stream>>>(map, p, L.k_pad / tc::BK, n_tiles, num_tiles,
+    tc::contraction_tf32x3_kernel<BN, MODE><<<grid, tc::NUM_THREADS, smem, stream>>>(packed, p, L.k_pad / tc::BK, n_tiles, num_tiles,
                                                                               status, diag, trace);
     DLP_LAUNCH_OK("contraction_tf32x3_kernel");
+#ifdef DLP_TC_DIAGNOSTICS
     if(trace) {
         static long long host[64 * 16];
         DLP_CUDA_OK(cudaStreamSynchronize(stream));
@@ -769,6 +796,7 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const CUtensorMap 
             fclose(f);
         }
     }
+#endif
     return DLP_OK;
 }
 } // namespace
@@ -776,22 +804,17 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const CUtensorMap 
 dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream)
 {
     if(p.rows <= 0 || p.cols <= 0) return DLP_OK;
-    EncodeTiledFn enc = encode_tiled();
-    if(!enc) return fail(DLP_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from the CUDA driver");
     if(reinterpret_cast<uintptr_t>(packed) % 16 != 0) return fail(DLP_INVALID_ARGUMENT, "packed weights must be 16-byte aligned");
-    CUtensorMap map;
-    const cuuint64_t dims[2] = { cuuint64_t(L.k_pad), cuuint64_t(L.n_pad) };
-    const cuuint64_t strides[1] = { cuuint64_t(L.k_pad) * sizeof(float) };
-    const cuuint32_t box[2] = { cuuint32_t(tc::BK), cuuint32_t(L.bn) };
-    const cuuint32_t elem[2] = { 1, 1 };
-    CUresult rc = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(packed), dims, strides, box, elem,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if(rc != CUDA_SUCCESS) return fail(DLP_CUDA_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(rc)));
-    switch(L.bn) {
-    case 32: return launch_bn<32>(p, L, map, stream);
-    case 64: return launch_bn<64>(p, L, map, stream);
-    case 128: return launch_bn<128>(p, L, map, stream);
+    switch(L.bn * 4 + p.a_mode) {
+    case 32 * 4 + A_GATHER: return launch_bn<32, A_GATHER>(p, L, packed, stream);
+    case 32 * 4 + A_STRIDED: return launch_bn<32, A_STRIDED>(p, L, packed, stream);
+    case 32 * 4 + A_TAPBLOCK: return launch_bn<32, A_TAPBLOCK>(p, L, packed, stream);
+    case 64 * 4 + A_GATHER: return launch_bn<64, A_GATHER>(p, L, packed, stream);
+    case 64 * 4 + A_STRIDED: return launch_bn<64, A_STRIDED>(p, L, packed, stream);
+    case 64 * 4 + A_TAPBLOCK: return launch_bn<64, A_TAPBLOCK>(p, L, packed, stream);
+    case 128 * 4 + A_GATHER: return launch_bn<128, A_GATHER>(p, L, packed, stream);
+    case 128 * 4 + A_STRIDED: return launch_bn<128, A_STRIDED>(p, L, packed, stream);
+    case 128 * 4 + A_TAPBLOCK: return launch_bn<128, A_TAPBLOCK>(p, L, packed, stream);
     }
     return fail(DLP_INVALID_ARGUMENT, "unsupported column tile");
 }

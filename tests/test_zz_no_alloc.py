@@ -43,7 +43,7 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row():
 
 def test_static_scratch_refuses_sizes_beyond_its_limit():
     from dlprimitives_b200 import capi
-    ip = capi.IPForward(8192, 1024, 4, bias=False)           # packed weights: 32 MiB > 16 MiB
+    ip = capi.IPForward(8192, 1024, 4, bias=False)           # packed weights: 64 MiB > 16 MiB
     x = torch.zeros(4, 8192, device=DEV)
     w = torch.zeros(1024, 8192, device=DEV)
     y = torch.zeros(4, 1024, device=DEV)
