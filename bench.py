@@ -348,12 +348,13 @@ def run_gpu_arm(args, rank, world, local_rank):
 
 def run_single_conv(args):
     """One convolution through the C ABI, repeated: the small case profiler captures are taken on.
-    --conv N,Cin,H,Cout,K,stride,pad[,groups]"""
+    --conv N,Cin,H,Cout,K,stride,pad[,groups[,residual]]   (residual = 1: the fused "+ residual, ReLU" form)"""
     import torch
     from dlprimitives_b200 import capi
     v = [int(t) for t in args.conv.split(",")]
     n, cin, hw, cout, k, stride, pad = v[:7]
     groups = v[7] if len(v) > 7 else 1
+    with_res = len(v) > 8 and v[8] != 0
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev)
     g.manual_seed(1)
@@ -363,19 +364,21 @@ def run_single_conv(args):
     plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, stride=stride, pad=pad, groups=groups, batch=n, height=hw, width=hw,
                               bias=True, activation="relu")
     y = torch.empty(plan.output_shape(n), device=dev)
+    res = torch.randn(plan.output_shape(n), device=dev, generator=g) if with_res else None
+    extra = dict(residual=res, post_activation="relu") if with_res else {}
     packed = plan.prepack(w)
     for _ in range(max(args.warmup, 3)):
-        plan.enqueue_packed(x, packed, b, y)
+        plan.enqueue_packed(x, packed, b, y, **extra)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        plan.enqueue_packed(x, packed, b, y)
+        plan.enqueue_packed(x, packed, b, y, **extra)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     flops = 2.0 * y.numel() * (cin // groups) * k * k
-    byts = 4.0 * (x.numel() + y.numel() + w.numel() + b.numel())
+    byts = 4.0 * (x.numel() + y.numel() * (2 if with_res else 1) + w.numel() + b.numel())
     print(json.dumps({"conv": args.conv, "algo": plan.algo(), "kernel": plan.kernel(), "ms": ms, "tflops": flops / ms / 1e9, "gbs": byts / ms / 1e6,
                       "gflop": flops / 1e9, "mbytes": byts / 1e6, "status": capi.device_status()}), flush=True)
 
@@ -387,7 +390,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--conv", default=None, help="profile one convolution instead: N,Cin,H,Cout,K,stride,pad[,groups]")
+    ap.add_argument("--conv", default=None, help="profile one convolution instead: N,Cin,H,Cout,K,stride,pad[,groups[,residual]]")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

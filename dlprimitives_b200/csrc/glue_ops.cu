@@ -38,6 +38,51 @@ __global__ void pooling2d_kernel(const float *__restrict__ x, float *__restrict_
     }
 }
 
+// Pooling of planes that fit in shared memory: one CTA per plane reads the plane once with coalesced
+// (16-byte when aligned) loads, then every thread computes outputs from shared memory.  The arithmetic is
+// the same as pooling2d_kernel's, in the same order.
+__global__ void pooling2d_plane_kernel(const float *__restrict__ x, float *__restrict__ y, int planes, int in_h, int in_w, int out_h,
+                                       int out_w, int kh, int kw, int sh, int sw, int ph, int pw, int mode_avg, int include_pad, int vec_ok)
+{
+    extern __shared__ float tile[];
+    const int in_plane = in_h * in_w, out_plane = out_h * out_w;
+    for(int plane = blockIdx.x; plane < planes; plane += gridDim.x) {
+        const float *src = x + (long long)plane * in_plane;
+        if(vec_ok) {
+            const float4 *src4 = reinterpret_cast<const float4 *>(src);
+            float4 *tile4 = reinterpret_cast<float4 *>(tile);
+            for(int i = threadIdx.x; i < in_plane / 4; i += blockDim.x) tile4[i] = __ldg(src4 + i);
+        }
+        else
+            for(int i = threadIdx.x; i < in_plane; i += blockDim.x) tile[i] = __ldg(src + i);
+        __syncthreads();
+        float *dst = y + (long long)plane * out_plane;
+        for(int i = threadIdx.x; i < out_plane; i += blockDim.x) {
+            const int orow = i / out_w, oc = i - orow * out_w;
+            int row0 = orow * sh - ph, col0 = oc * sw - pw;
+            int row1 = row0 + kh, col1 = col0 + kw;
+            const int dr_pad = min(row1, in_h + ph) - max(-ph, row0);
+            const int dc_pad = min(col1, in_w + pw) - max(-pw, col0);
+            row0 = max(row0, 0); col0 = max(col0, 0);
+            row1 = min(row1, in_h); col1 = min(col1, in_w);
+            float val = mode_avg ? 0.0f : -FLT_MAX;
+            for(int r = row0; r < row1; r++)
+                for(int c = col0; c < col1; c++) {
+                    const float v = tile[r * in_w + c];
+                    val = mode_avg ? val + v : fmaxf(val, v);
+                }
+            if(mode_avg) {
+                const int dr = row1 - row0, dc = col1 - col0;
+                if(dr == kh && dc == kw) val = val * (1.0f / (kh * kw));
+                else if(include_pad) val = val / float(dr_pad * dc_pad);
+                else val = val * (1.0f / (dr * dc));
+            }
+            dst[i] = val;
+        }
+        __syncthreads();
+    }
+}
+
 // one warp per plane
 __global__ void global_pooling_kernel(const float *__restrict__ x, float *__restrict__ y, int planes, int plane_size, int mode_avg)
 {
@@ -177,6 +222,21 @@ dlp_status dlp_pooling2d_fwd(const float *x, float *y, int planes, int in_h, int
     DLP_REQUIRE(mode == 0 || mode == 1, "mode must be 0 (max) or 1 (avg)");
     const long long total = (long long)planes * oh * ow;
     if(total <= 0) return DLP_OK;
+    const size_t plane_bytes = size_t(in_h) * in_w * sizeof(float);
+    if(plane_bytes <= 56 * 1024 && oh * ow >= 256) {
+        // whole planes through shared memory: each input byte is read from memory once, in full lines
+        static bool configured = false;
+        if(!configured) {
+            DLP_CUDA_OK(cudaFuncSetAttribute(pooling2d_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 56 * 1024));
+            configured = true;
+        }
+        const int vec_ok = (in_h * in_w) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+        const int grid = std::min(planes, sm_count() * 4);
+        pooling2d_plane_kernel<<<grid, 512, plane_bytes, (cudaStream_t)stream>>>(x, y, planes, in_h, in_w, oh, ow, kernel[0], kernel[1], stride[0],
+                                                                                 stride[1], pad[0], pad[1], mode, count_include_pad, vec_ok);
+        DLP_LAUNCH_OK("pooling2d_plane_kernel");
+        return DLP_OK;
+    }
     pooling2d_kernel<<<grid_for(size_t(total), 256), 256, 0, (cudaStream_t)stream>>>(x, y, total, in_h, in_w, oh, ow, kernel[0], kernel[1],
                                                                                       stride[0], stride[1], pad[0], pad[1], mode,
                                                                                       count_include_pad);
