@@ -55,7 +55,7 @@ enum { ST_TMA_EMPTY = 101, ST_MMA_FULL_B = 102, ST_MMA_FULL_A = 103, ST_MMA_ACC 
 // Diagnostics are compiled in only with -DDLP_TC_DIAGNOSTICS (the hot loops are tight and share a small
 // instruction cache): the timeline (environment variable DLP_TC_TRACE=<file>) and the switches below
 // (environment variable DLP_TC_DIAG, for timing experiments; results are wrong with any set).
-enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4, DIAG_NO_EPILOGUE = 8 };
+enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4 };
 
 struct Shared {
     unsigned long long full_b[STAGES];         // the bulk copy of a k-block's B tiles landed
@@ -264,22 +264,21 @@ __device__ __forceinline__ float2 act_clamp(int act)
     return make_float2(act == DLP_ACT_IDENTITY ? -INFINITY : 0.0f, act == DLP_ACT_RELU6 ? 6.0f : INFINITY);
 }
 // Lean store of N output columns of one row: y = clamp(acc + bias) [then clamp(y + s*residual)].
-// Columns are cs elements apart; indexing with a 32-bit product keeps every address one independent
-// multiply-add instead of a link in a chain of 64-bit increments.
 template<int N, bool BIAS, bool RES>
-__device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const float (&res)[N], int cs, const float (&bias)[N],
+__device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const float (&res)[N], long long cs, const float *b0,
                                            float2 clamp, float res_scale, float2 post_clamp)
 {
     #pragma unroll
     for(int j = 0; j < N; j++) {
         float a = v[j];
-        if(BIAS) a += bias[j];
+        if(BIAS) a += __ldg(b0 + j);
         a = fminf(fmaxf(a, clamp.x), clamp.y);
         if(RES) {
             a = a + res_scale * res[j];
             a = fminf(fmaxf(a, post_clamp.x), post_clamp.y);
         }
-        y0[j * cs] = a;
+        *y0 = a;
+        y0 += cs;
     }
 }
 
@@ -459,23 +458,19 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         // identity / relu / relu6 are a clamp; with no per-row bias and no beta the whole epilogue is
         // add, clamp, (residual, clamp,) store.  Anything else takes the general path.
         const float2 clamp = act_clamp(p.act), post_clamp = act_clamp(p.post_act);
-        // (and the columns of a tile must be within 32-bit element offsets of each other)
-        const bool epi_fast = act_is_clamp(p.act) && act_is_clamp(p.post_act) && p.bias_mode != DLP_GEMM_BIAS_M && p.beta == 0.0f &&
-                              (p.out_mode != OUT_NCHW || (long long)p.plane * BN < (1ll << 30));
-        const bool bias_vec = (reinterpret_cast<uintptr_t>(p.bias) & 15) == 0;
+        const bool epi_fast = act_is_clamp(p.act) && act_is_clamp(p.post_act) && p.bias_mode != DLP_GEMM_BIAS_M && p.beta == 0.0f;
         bool live = true;
         for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
             const int n0 = int(tile % n_tiles) * BN;
             const long long row = (tile / n_tiles) * BM + row_in_tile;
             const RowInfo r = make_row(p, row);
-            const int col_stride = p.out_mode == OUT_NCHW ? p.plane : 1;
+            const long long col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : 1ll;
             // The tile is handled 32 columns at a time: two tensor-memory loads under one wait; on the last
-            // chunk the bias and the residual operand of the same columns are fetched under that wait as well.
+            // chunk the residual operand of the same columns is fetched under that wait as well.
             constexpr int G = BN >= 32 ? 32 : 16;
             constexpr int GROUPS = BN / G;
             const bool fast = epi_fast && r.valid && n0 + BN <= p.cols && !TC_DIAG(DIAG_NO_STORES);
             const bool with_res = fast && p.residual != nullptr;
-            const bool with_bias = fast && p.bias_mode == DLP_GEMM_BIAS_N;
             float *y_row = p.y + r.out + (long long)n0 * col_stride;
             const float *res_row = with_res ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
             for(int c = 0; c < chunks_per_tile; c++, chunk++) {
@@ -487,30 +482,15 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 #pragma unroll 1
                 for(int g = 0; g < GROUPS; g++) {
                     uint32_t v[G];
-                    float res[G], bias[G];
-                    const int col0 = n0 + g * G;
+                    float res[G];
                     __syncwarp();
                     if(quad == 0 && lane == 0) TC_TRACE(9, chunk * GROUPS + g);
                     tmem_ld(taddr + g * G, v);
-                    if(last && with_bias) {
-                        if(bias_vec) {
-                            const float4 *b4 = reinterpret_cast<const float4 *>(p.bias + col0);
-                            #pragma unroll
-                            for(int j = 0; j < G / 4; j++) {
-                                const float4 t = __ldg(b4 + j);
-                                bias[4 * j] = t.x; bias[4 * j + 1] = t.y; bias[4 * j + 2] = t.z; bias[4 * j + 3] = t.w;
-                            }
-                        }
-                        else {
-                            #pragma unroll
-                            for(int j = 0; j < G; j++) bias[j] = __ldg(p.bias + col0 + j);
-                        }
-                    }
                     if(last && with_res) {
                         // the residual operand of these columns travels while the tensor-memory load does
-                        const float *rp = res_row + g * G * col_stride;
+                        const float *rp = res_row + (long long)(g * G) * col_stride;
                         #pragma unroll
-                        for(int j = 0; j < G; j++) res[j] = __ldg(rp + j * col_stride);
+                        for(int j = 0; j < G; j++) { res[j] = __ldg(rp); rp += col_stride; }
                     }
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if(quad == 0 && lane == 0) TC_TRACE(10, chunk * GROUPS + g);
@@ -522,30 +502,25 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                     }
                     float x[G];
                     float *sg = my_sums + g * G * BM;
-                    if(first) {
-                        #pragma unroll
-                        for(int j = 0; j < G; j++) x[j] = __uint_as_float(v[j]);
-                    }
-                    else {
-                        #pragma unroll
-                        for(int j = 0; j < G; j++) x[j] = sg[j * BM] + __uint_as_float(v[j]);
-                    }
+                    #pragma unroll
+                    for(int j = 0; j < G; j++) x[j] = first ? __uint_as_float(v[j]) : sg[j * BM] + __uint_as_float(v[j]);
                     if(!last) {
                         #pragma unroll
                         for(int j = 0; j < G; j++) sg[j * BM] = x[j];
                         continue;
                     }
                     // ---- last chunk: these columns of the row are final
-                    if(TC_DIAG(DIAG_NO_EPILOGUE)) { }
-                    else if(fast) {
-                        float *y0 = y_row + g * G * col_stride;
+                    const int col0 = n0 + g * G;
+                    if(fast) {
+                        float *y0 = y_row + (long long)(g * G) * col_stride;
+                        const float *b0 = p.bias + col0;
                         if(with_res) {
-                            if(with_bias) store_cols<G, true, true>(x, y0, res, col_stride, bias, clamp, p.residual_scale, post_clamp);
-                            else store_cols<G, false, true>(x, y0, res, col_stride, bias, clamp, p.residual_scale, post_clamp);
+                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp);
+                            else store_cols<G, false, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp);
                         }
                         else {
-                            if(with_bias) store_cols<G, true, false>(x, y0, res, col_stride, bias, clamp, 0.0f, post_clamp);
-                            else store_cols<G, false, false>(x, y0, res, col_stride, bias, clamp, 0.0f, post_clamp);
+                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp);
+                            else store_cols<G, false, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp);
                         }
                     }
                     else {
@@ -574,7 +549,6 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         RowInfo r;
         r.valid = false; r.base = 0; r.iy0 = r.ix0 = 0; r.out = 0;
 
-        const int k_stride = int(p.a_k_stride);          // element distance of consecutive k (checked on the host to fit)
         const bool row_vec = MODE == A_STRIDED && p.plane == 0 && p.a_k_stride == 1 && (p.a_row_stride & 3) == 0 &&
                              (reinterpret_cast<uintptr_t>(p.a) & 15) == 0;
         auto advance = [&](Cursor &c, int steps) {
@@ -614,13 +588,13 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 }
                 else if(r.valid && k0 + BK <= p.k) {
                     #pragma unroll
-                    for(int i = 0; i < BK; i++) buf[i] = __ldg(src + i * k_stride);
+                    for(int i = 0; i < BK; i++) buf[i] = __ldg(src + (long long)i * p.a_k_stride);
                 }
                 else {
                     #pragma unroll
                     for(int i = 0; i < BK; i++) {
                         const bool ok = r.valid && (k0 + i) < p.k;
-                        buf[i] = ok ? __ldg(src + i * k_stride) : 0.0f;
+                        buf[i] = ok ? __ldg(src + (long long)i * p.a_k_stride) : 0.0f;
                     }
                 }
             }
@@ -630,7 +604,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 const float *src = p.a + r.base + (long long)(cb * BK) * p.a_k_stride + (d >> 16) * p.in_w + (d & 0xffff);
                 if((tap_mask >> t) & 1ull) {
                     #pragma unroll
-                    for(int i = 0; i < BK; i++) buf[i] = __ldg(src + i * k_stride);
+                    for(int i = 0; i < BK; i++) buf[i] = __ldg(src + (long long)i * p.a_k_stride);
                 }
                 else {
                     #pragma unroll
@@ -842,7 +816,6 @@ dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const 
 {
     if(p.rows <= 0 || p.cols <= 0) return DLP_OK;
     if(reinterpret_cast<uintptr_t>(packed) % 16 != 0) return fail(DLP_INVALID_ARGUMENT, "packed weights must be 16-byte aligned");
-    if(p.a_k_stride < 0 || p.a_k_stride >= (1ll << 25)) return fail(DLP_INVALID_ARGUMENT, "k stride of the A operand out of range");
     switch(L.bn * 4 + p.a_mode) {
     case 32 * 4 + A_GATHER: return launch_bn<32, A_GATHER>(p, L, packed, stream);
     case 32 * 4 + A_STRIDED: return launch_bn<32, A_STRIDED>(p, L, packed, stream);
