@@ -362,7 +362,7 @@ def run_single_conv(args):
     w = torch.randn(cout, cin // groups, k, k, device=dev, generator=g) * (2.0 / (cin // groups * k * k)) ** 0.5
     b = torch.rand(cout, device=dev, generator=g) * 0.2 - 0.1
     plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, stride=stride, pad=pad, groups=groups, batch=n, height=hw, width=hw,
-                              bias=True, activation="relu")
+                              bias=True, activation="relu", algo=args.conv_algo)
     y = torch.empty(plan.output_shape(n), device=dev)
     res = torch.randn(plan.output_shape(n), device=dev, generator=g) if with_res else None
     extra = dict(residual=res, post_activation="relu") if with_res else {}
@@ -390,6 +390,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--conv-algo", default="", help="algorithm request for --conv: '', gemm, winograd, depthwise_separable")
     ap.add_argument("--conv", default=None, help="profile one convolution instead: N,Cin,H,Cout,K,stride,pad[,groups[,residual]]")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -160,9 +160,16 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
         plan->kind = CK_DEPTHWISE;
         plan->kernel = "depthwise_k" + std::to_string(d.kernel[0]) + "_s" + std::to_string(d.stride[0]);
     }
+    else if(algo == "winograd" && square && d.groups == 1 && d.dilate[0] == 1 && d.stride[0] == 1 && d.kernel[0] == 3 && d.pad[0] == 1) {
+        // Only on request.  The reference also takes Winograd under "auto" (src/core/conv.cpp:713-720); here
+        // the 3xTF32 tensor-core implicit GEMM is the faster kernel for every eligible shape, so "auto" keeps it.
+        plan->algo = "winograd";
+        plan->kind = CK_WINOGRAD;
+        plan->kernel = "winograd_f23_ffma";
+    }
     else {
-        // "winograd" requests land here until the Winograd kernels exist: like the reference does for
-        // an incompatible request (src/core/conv.cpp:719-727), the plan substitutes the GEMM algorithm.
+        // an incompatible "winograd" or "depthwise_separable" request gets the GEMM algorithm, as in the
+        // reference (src/core/conv.cpp:719-727)
         plan->algo = "gemm";
         // the tensor-core loader keeps one validity bit per kernel tap in a 64-bit word
         const bool tc_ok = d.groups == 1 && d.math_mode != DLP_MATH_FP32_FFMA && d.kernel[0] * d.kernel[1] <= MAX_TAPS;
@@ -173,7 +180,7 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
     plan->strided_a = d.kernel[0] == 1 && d.kernel[1] == 1 && d.stride[0] == 1 && d.stride[1] == 1 && d.pad[0] == 0 && d.pad[1] == 0;
 
     plan->tapblock = plan->kind == CK_TC && !plan->strided_a && d.channels_in % 32 == 0;
-    if(plan->kind != CK_DEPTHWISE) {
+    if(plan->kind != CK_DEPTHWISE && plan->kind != CK_WINOGRAD) {
         plan->packed = tc_packed_layout(d.channels_out / d.groups, plan->k);
         if(plan->kind == CK_TC)
             plan->kernel = std::string("igemm_tf32x3_bn") + std::to_string(plan->packed.bn) + (plan->strided_a ? "_1x1" : (plan->tapblock ? "_taps" : "_gather"));
@@ -220,12 +227,21 @@ void dlp_conv2d_fwd_destroy(dlp_conv2d_plan *plan)
 }
 const char *dlp_conv2d_fwd_algo(const dlp_conv2d_plan *plan) { return plan ? plan->algo.c_str() : ""; }
 const char *dlp_conv2d_fwd_kernel(const dlp_conv2d_plan *plan) { return plan ? plan->kernel.c_str() : ""; }
-size_t dlp_conv2d_fwd_packed_bytes(const dlp_conv2d_plan *plan) { return plan && plan->kind == CK_TC ? plan->packed.bytes() : 0; }
+size_t dlp_conv2d_fwd_packed_bytes(const dlp_conv2d_plan *plan)
+{
+    if(!plan) return 0;
+    if(plan->kind == CK_WINOGRAD) return winograd_packed_bytes(plan->d.channels_in, plan->d.channels_out);
+    return plan->kind == CK_TC ? plan->packed.bytes() : 0;
+}
 size_t dlp_conv2d_fwd_workspace(const dlp_conv2d_plan *plan) { return dlp_conv2d_fwd_packed_bytes(plan); }
 
 dlp_status dlp_conv2d_fwd_prepack(const dlp_conv2d_plan *plan, const float *w, void *packed, void *stream)
 {
     DLP_REQUIRE(plan && w, "null argument");
+    if(plan->kind == CK_WINOGRAD) {
+        DLP_REQUIRE(packed != nullptr, "null packed buffer");
+        return winograd_filter_transform(w, static_cast<float *>(packed), plan->d.channels_in, plan->d.channels_out, (cudaStream_t)stream);
+    }
     if(plan->kind != CK_TC) return DLP_OK;
     DLP_REQUIRE(packed != nullptr, "null packed buffer");
     return tc_prepack(plan->packed, w, plan->k, 1, plan->d.channels_out, plan->k, static_cast<float *>(packed),
@@ -250,6 +266,12 @@ static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, cons
         DLP_REQUIRE(residual == nullptr, "the depthwise kernel has no fused residual");
         return launch_depthwise(x, w_raw, bias, y, batch, d.channels_in, d.height, d.width, d.kernel[0], d.stride[0], d.pad[0],
                                 d.activation, factor, stream);
+    }
+
+    if(plan->kind == CK_WINOGRAD) {
+        DLP_REQUIRE(packed != nullptr, "null transformed filters");
+        return launch_winograd_f23(x, packed, bias, y, batch, d.channels_in, d.channels_out, d.height, d.width, d.activation, factor,
+                                   residual, residual_scale, post_act, stream);
     }
 
     const int cin_g = d.channels_in / d.groups, cout_g = d.channels_out / d.groups;
@@ -306,10 +328,10 @@ dlp_status dlp_conv2d_fwd_enqueue(const dlp_conv2d_plan *plan, const float *x, c
     if(batch == 0) return DLP_OK;      // an empty batch is valid and launches nothing
     DLP_REQUIRE(w != nullptr, "null weights");
     const float *packed = nullptr;
-    if(plan->kind == CK_TC) {
-        // the weights are split into their TF32 hi/lo planes in the caller's workspace on every call,
-        // as the reference redoes its Winograd filter transform on every call
-        DLP_REQUIRE(ws != nullptr && ws_bytes >= plan->packed.bytes(), "workspace smaller than dlp_conv2d_fwd_workspace()");
+    if(plan->kind == CK_TC || plan->kind == CK_WINOGRAD) {
+        // the weights are packed (split into TF32 hi/lo stages, or Winograd-transformed) in the caller's
+        // workspace on every call, as the reference redoes its Winograd filter transform on every call
+        DLP_REQUIRE(ws != nullptr && ws_bytes >= dlp_conv2d_fwd_packed_bytes(plan), "workspace smaller than dlp_conv2d_fwd_workspace()");
         dlp_status st = dlp_conv2d_fwd_prepack(plan, w, ws, stream);
         if(st != DLP_OK) return st;
         packed = static_cast<const float *>(ws);
@@ -327,8 +349,9 @@ dlp_status dlp_conv2d_fwd_enqueue_packed(const dlp_conv2d_plan *plan, const floa
     if(batch == 0) return DLP_OK;
     DLP_REQUIRE(packed != nullptr, "null weights");
     // plans whose kernel reads raw weights take them through the same argument
-    const float *raw = plan->kind == CK_TC ? nullptr : static_cast<const float *>(packed);
-    const float *pk = plan->kind == CK_TC ? static_cast<const float *>(packed) : nullptr;
+    const bool takes_packed = plan->kind == CK_TC || plan->kind == CK_WINOGRAD;
+    const float *raw = takes_packed ? nullptr : static_cast<const float *>(packed);
+    const float *pk = takes_packed ? static_cast<const float *>(packed) : nullptr;
     if(residual && plan->kind == CK_DEPTHWISE) return fail(DLP_NOT_IMPLEMENTED, "the depthwise kernel has no fused residual");
     return conv_enqueue(plan, x, raw, pk, bias, y, factor, residual, residual_scale, post_activation, batch, in_h, in_w,
                         (cudaStream_t)stream);

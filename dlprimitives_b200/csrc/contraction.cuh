@@ -133,4 +133,10 @@ dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride,
                       float *packed, int taps, cudaStream_t stream);
 dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream);
 
+// Winograd F(2x2, 3x3), stride 1, padding 1 (winograd.cu).  u: the transformed filters, winograd_packed_bytes() long.
+size_t winograd_packed_bytes(int cin, int cout);
+dlp_status winograd_filter_transform(const float *w, float *u, int cin, int cout, cudaStream_t stream);
+dlp_status launch_winograd_f23(const float *x, const float *u, const float *bias, float *y, int batch, int cin, int cout, int h, int w,
+                               int act, float factor, const float *residual, float residual_scale, int post_act, cudaStream_t stream);
+
 } // namespace dlp

@@ -38,28 +38,34 @@ __global__ void pooling2d_kernel(const float *__restrict__ x, float *__restrict_
     }
 }
 
-// Pooling of planes that fit in shared memory: one CTA per plane reads the plane once with coalesced
-// (16-byte when aligned) loads, then every thread computes outputs from shared memory.  The arithmetic is
-// the same as pooling2d_kernel's, in the same order.
-__global__ void pooling2d_plane_kernel(const float *__restrict__ x, float *__restrict__ y, int planes, int in_h, int in_w, int out_h,
-                                       int out_w, int kh, int kw, int sh, int sw, int ph, int pw, int mode_avg, int include_pad, int vec_ok)
+// Pooling through shared memory: a CTA takes a band of output rows of one plane, reads the input rows
+// the band needs once with coalesced (16-byte when aligned) loads, then every thread computes outputs
+// from shared memory.  The arithmetic is the same as pooling2d_kernel's, in the same order.
+__global__ void pooling2d_band_kernel(const float *__restrict__ x, float *__restrict__ y, long long bands_total, int bands_per_plane,
+                                      int band_rows, int in_h, int in_w, int out_h, int out_w, int kh, int kw, int sh, int sw, int ph,
+                                      int pw, int mode_avg, int include_pad, int vec_ok)
 {
     extern __shared__ float tile[];
-    const int in_plane = in_h * in_w, out_plane = out_h * out_w;
-    for(int plane = blockIdx.x; plane < planes; plane += gridDim.x) {
-        const float *src = x + (long long)plane * in_plane;
+    for(long long band = blockIdx.x; band < bands_total; band += gridDim.x) {
+        const long long plane = band / bands_per_plane;
+        const int orow0 = int(band - plane * bands_per_plane) * band_rows;
+        const int orows = min(band_rows, out_h - orow0);
+        const int irow0 = max(orow0 * sh - ph, 0), irow1 = min((orow0 + orows - 1) * sh - ph + kh, in_h);
+        const float *src = x + plane * (long long)in_h * in_w + (long long)irow0 * in_w;
+        const int count = (irow1 - irow0) * in_w;
         if(vec_ok) {
+            // in_w is a multiple of 4 and x is 16-byte aligned, so every row starts on a 16-byte boundary
             const float4 *src4 = reinterpret_cast<const float4 *>(src);
             float4 *tile4 = reinterpret_cast<float4 *>(tile);
-            for(int i = threadIdx.x; i < in_plane / 4; i += blockDim.x) tile4[i] = __ldg(src4 + i);
+            for(int i = threadIdx.x; i < count / 4; i += blockDim.x) tile4[i] = __ldg(src4 + i);
         }
         else
-            for(int i = threadIdx.x; i < in_plane; i += blockDim.x) tile[i] = __ldg(src + i);
+            for(int i = threadIdx.x; i < count; i += blockDim.x) tile[i] = __ldg(src + i);
         __syncthreads();
-        float *dst = y + (long long)plane * out_plane;
-        for(int i = threadIdx.x; i < out_plane; i += blockDim.x) {
-            const int orow = i / out_w, oc = i - orow * out_w;
-            int row0 = orow * sh - ph, col0 = oc * sw - pw;
+        float *dst = y + plane * (long long)out_h * out_w + (long long)orow0 * out_w;
+        for(int i = threadIdx.x; i < orows * out_w; i += blockDim.x) {
+            const int orel = i / out_w, oc = i - orel * out_w;
+            int row0 = (orow0 + orel) * sh - ph, col0 = oc * sw - pw;
             int row1 = row0 + kh, col1 = col0 + kw;
             const int dr_pad = min(row1, in_h + ph) - max(-ph, row0);
             const int dc_pad = min(col1, in_w + pw) - max(-pw, col0);
@@ -68,7 +74,7 @@ __global__ void pooling2d_plane_kernel(const float *__restrict__ x, float *__res
             float val = mode_avg ? 0.0f : -FLT_MAX;
             for(int r = row0; r < row1; r++)
                 for(int c = col0; c < col1; c++) {
-                    const float v = tile[r * in_w + c];
+                    const float v = tile[(r - irow0) * in_w + c];
                     val = mode_avg ? val + v : fmaxf(val, v);
                 }
             if(mode_avg) {
@@ -222,20 +228,25 @@ dlp_status dlp_pooling2d_fwd(const float *x, float *y, int planes, int in_h, int
     DLP_REQUIRE(mode == 0 || mode == 1, "mode must be 0 (max) or 1 (avg)");
     const long long total = (long long)planes * oh * ow;
     if(total <= 0) return DLP_OK;
-    const size_t plane_bytes = size_t(in_h) * in_w * sizeof(float);
-    if(plane_bytes <= 56 * 1024 && oh * ow >= 256) {
-        // whole planes through shared memory: each input byte is read from memory once, in full lines
-        static bool configured = false;
-        if(!configured) {
-            DLP_CUDA_OK(cudaFuncSetAttribute(pooling2d_plane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 56 * 1024));
-            configured = true;
+    // Bands of output rows through shared memory when a useful band fits in 12 KB: each input byte is read
+    // from memory once (plus the halo rows between bands), in full lines.
+    {
+        const size_t row_bytes = size_t(in_w) * sizeof(float);
+        int band_rows = 0;
+        for(int r = std::min(oh, 16); r >= 1; r--)
+            if((size_t(r - 1) * stride[0] + kernel[0]) * row_bytes <= 12 * 1024) { band_rows = r; break; }
+        if(band_rows >= 2 && ow >= 16) {
+            const int bands_per_plane = (oh + band_rows - 1) / band_rows;
+            const long long bands_total = (long long)planes * bands_per_plane;
+            const size_t smem = (size_t(band_rows - 1) * stride[0] + kernel[0]) * row_bytes;
+            const int vec_ok = in_w % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+            const int grid = int(std::min<long long>(bands_total, (long long)sm_count() * 16));
+            pooling2d_band_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(x, y, bands_total, bands_per_plane, band_rows, in_h, in_w, oh, ow,
+                                                                             kernel[0], kernel[1], stride[0], stride[1], pad[0], pad[1], mode,
+                                                                             count_include_pad, vec_ok);
+            DLP_LAUNCH_OK("pooling2d_band_kernel");
+            return DLP_OK;
         }
-        const int vec_ok = (in_h * in_w) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
-        const int grid = std::min(planes, sm_count() * 4);
-        pooling2d_plane_kernel<<<grid, 512, plane_bytes, (cudaStream_t)stream>>>(x, y, planes, in_h, in_w, oh, ow, kernel[0], kernel[1], stride[0],
-                                                                                 stride[1], pad[0], pad[1], mode, count_include_pad, vec_ok);
-        DLP_LAUNCH_OK("pooling2d_plane_kernel");
-        return DLP_OK;
     }
     pooling2d_kernel<<<grid_for(size_t(total), 256), 256, 0, (cudaStream_t)stream>>>(x, y, total, in_h, in_w, oh, ow, kernel[0], kernel[1],
                                                                                       stride[0], stride[1], pad[0], pad[1], mode,

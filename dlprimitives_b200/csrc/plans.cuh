@@ -6,7 +6,7 @@
 using dlp::KTap;
 using dlp::TcPacked;
 
-enum ConvKernel { CK_TC, CK_FFMA, CK_DEPTHWISE };
+enum ConvKernel { CK_TC, CK_FFMA, CK_DEPTHWISE, CK_WINOGRAD };
 
 struct dlp_conv2d_plan {
     dlp_conv2d_desc d;

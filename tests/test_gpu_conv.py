@@ -209,6 +209,11 @@ def test_algorithm_selection_follows_the_reference_rules():
     assert mk(channels_in=16, channels_out=16, kernel=3, pad=1, groups=16, stride=2, algo="depthwise_separable").algo() == "gemm"
     assert mk(channels_in=16, channels_out=32, kernel=3, pad=1, groups=16).algo() == "gemm"     # channel multiplier: not handled as depthwise
     assert mk(channels_in=16, channels_out=16, kernel=3, pad=0, algo="winograd").algo() == "gemm"
+    assert mk(channels_in=16, channels_out=16, kernel=3, pad=1, stride=2, algo="winograd").algo() == "gemm"
+    win = mk(channels_in=16, channels_out=16, kernel=3, pad=1, algo="winograd")
+    assert win.algo() == "winograd" and win.kernel() == "winograd_f23_ffma"
+    assert win.workspace() >= 16 * 16 * 16 * 4          # the reference's 16*Cin*Cout floats (src/core/conv.cpp:229-232)
+    assert mk(channels_in=16, channels_out=16, kernel=3, pad=1).algo() == "gemm"    # "auto" keeps the tensor-core kernel here
     assert mk(channels_in=16, channels_out=16, kernel=1).algo() == "gemm"
     assert mk(channels_in=16, channels_out=16, kernel=1).kernel().startswith("igemm_tf32x3")
     assert mk(channels_in=16, channels_out=16, kernel=3, groups=2).kernel().startswith("igemm_ffma")
@@ -236,3 +241,32 @@ def test_errors_are_reported_not_swallowed():
     assert e.value.kind == "ValidationError"
     # empty batch: nothing to do, no launch, no error
     plan.enqueue(torch.zeros(0, 8, 8, 8, device=DEV), w, torch.zeros(8, device=DEV), torch.zeros(0, 8, 8, 8, device=DEV), ws)
+
+
+@pytest.mark.parametrize("cin,hw,cout,batch", [(64, 56, 64, 4), (128, 28, 128, 8), (256, 14, 256, 8), (512, 7, 512, 16), (24, 13, 40, 3)])
+def test_winograd_config_shapes(cin, hw, cout, batch):
+    """The Winograd benchmark configuration's shapes (and one with odd sizes and ragged channel counts)
+    against the CPU checker: plain call with factor, packed call with the fused residual."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    ob.set_threads(16)
+    rng = np.random.default_rng(cin * 1000 + hw)
+    x = rng.standard_normal((batch, cin, hw, hw), dtype=np.float32)
+    w = kaiming(rng, (cout, cin, 3, 3))
+    b = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+    plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=3, stride=1, pad=1, batch=batch, height=hw, width=hw,
+                              bias=True, activation="relu", algo="winograd")
+    assert plan.algo() == "winograd"
+    xd, wd, bd = to_dev(x), to_dev(w), to_dev(b)
+    want = ob.conv2d(x, w, b, stride=1, pad=1, activation="relu")
+    y0 = rng.standard_normal(want.shape, dtype=np.float32)
+    y = to_dev(y0)
+    ws = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=DEV)
+    plan.enqueue(xd, wd, bd, y, ws, factor=0.5)
+    assert rel_err(y.cpu().numpy(), want + 0.5 * y0) <= REL_TOL
+    res = rng.standard_normal(want.shape, dtype=np.float32)
+    packed = plan.prepack(wd)
+    y2 = torch.full(plan.output_shape(batch), float("nan"), device=DEV)
+    plan.enqueue_packed(xd, packed, bd, y2, residual=to_dev(res), residual_scale=1.0, post_activation="relu")
+    assert rel_err(y2.cpu().numpy(), np.maximum(want + res, 0.0)) <= REL_TOL
+    assert capi.device_status() == 0
