@@ -78,7 +78,7 @@ SYMBOLS = {
     "dlp_ip_fwd_packed_bytes": (_sz, [_vp]),
     "dlp_ip_fwd_prepack": (_i, [_vp, _fp, _vp, _vp]),
     "dlp_ip_fwd_enqueue": (_i, [_vp, _fp, _fp, _fp, _fp, _vp, _sz, _i, _vp]),
-    "dlp_ip_fwd_enqueue_packed": (_i, [_vp, _fp, _vp, _fp, _fp, _i, _vp]),
+    "dlp_ip_fwd_enqueue_packed": (_i, [_vp, _fp, _vp, _fp, _fp, _vp, _sz, _i, _vp]),
     "dlp_ip_fwd_enqueue_static": (_i, [_vp, _fp, _fp, _fp, _fp, _i, _vp]),
     "dlp_pooling2d_output_shape": (_i, [_i, _i, _i2, _i2, _i2, _i, _ip, _ip]),
     "dlp_pooling2d_fwd": (_i, [_fp, _fp, _i, _i, _i, _i2, _i2, _i2, _i, _i, _i, _vp]),
@@ -214,8 +214,10 @@ class Conv2DForward:
         self.packed = buf
         return buf
 
-    def enqueue_packed(self, x, packed, bias, y, factor=0.0, residual=None, residual_scale=1.0, post_activation="identity", stream=None):
-        check(lib().dlp_conv2d_fwd_enqueue_packed(self.h, _ptr(x), _ptr(packed), _ptr(bias), _ptr(y), None, 0, float(factor),
+    def enqueue_packed(self, x, packed, bias, y, factor=0.0, residual=None, residual_scale=1.0, post_activation="identity", stream=None,
+                       ws=None):
+        ws_bytes = ws.numel() * ws.element_size() if ws is not None else 0
+        check(lib().dlp_conv2d_fwd_enqueue_packed(self.h, _ptr(x), _ptr(packed), _ptr(bias), _ptr(y), _ptr(ws), ws_bytes, float(factor),
                                                   _ptr(residual), float(residual_scale), _act(post_activation),
                                                   x.shape[0], x.shape[2], x.shape[3], _stream(stream)))
 
@@ -286,8 +288,10 @@ class IPForward:
         check(lib().dlp_ip_fwd_prepack(self.h, _ptr(w), _ptr(buf), _stream(stream)))
         return buf
 
-    def enqueue_packed(self, x, packed, bias, y, stream=None):
-        check(lib().dlp_ip_fwd_enqueue_packed(self.h, _ptr(x), _ptr(packed), _ptr(bias), _ptr(y), x.shape[0], _stream(stream)))
+    def enqueue_packed(self, x, packed, bias, y, stream=None, ws=None):
+        ws_bytes = ws.numel() * ws.element_size() if ws is not None else 0
+        check(lib().dlp_ip_fwd_enqueue_packed(self.h, _ptr(x), _ptr(packed), _ptr(bias), _ptr(y), _ptr(ws), ws_bytes, x.shape[0],
+                                              _stream(stream)))
 
     def enqueue_static(self, x, w, bias, y, stream=None):
         """The allocation-free variant: scratch is the library's own fixed device array (no workspace)."""

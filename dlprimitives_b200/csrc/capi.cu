@@ -118,6 +118,17 @@ dlp_status dlp_device_status(void *stream, int *code)
     return DLP_OK;
 }
 
+// Workspace layout of the calls that pack their weights themselves: packed operand first, then (256-byte
+// aligned) the scratch that lets the tensor-core launcher split K.  The *_packed calls use their whole
+// workspace as that scratch.
+static size_t align256(size_t n) { return (n + 255) & ~size_t(255); }
+static void scratch_after(void *ws, size_t ws_bytes, size_t first_bytes, void *&scratch, size_t &scratch_bytes)
+{
+    const size_t off = align256(first_bytes);
+    scratch = ws && ws_bytes > off ? static_cast<char *>(ws) + off : nullptr;
+    scratch_bytes = scratch ? ws_bytes - off : 0;
+}
+
 // ---------------------------------------------------------------------------------------------- convolution
 dlp_status dlp_conv2d_output_shape(const dlp_conv2d_desc *desc, int in_h, int in_w, int *out_h, int *out_w)
 {
@@ -233,7 +244,13 @@ size_t dlp_conv2d_fwd_packed_bytes(const dlp_conv2d_plan *plan)
     if(plan->kind == CK_WINOGRAD) return winograd_packed_bytes(plan->d.channels_in, plan->d.channels_out);
     return plan->kind == CK_TC ? plan->packed.bytes() : 0;
 }
-size_t dlp_conv2d_fwd_workspace(const dlp_conv2d_plan *plan) { return dlp_conv2d_fwd_packed_bytes(plan); }
+size_t dlp_conv2d_fwd_workspace(const dlp_conv2d_plan *plan)
+{
+    const size_t packed = dlp_conv2d_fwd_packed_bytes(plan);
+    if(!plan || plan->kind != CK_TC) return packed;
+    const size_t split = tc_split_scratch_bytes((long long)plan->d.batch * plan->out_h * plan->out_w, plan->packed);
+    return split ? align256(packed) + split : packed;
+}
 
 dlp_status dlp_conv2d_fwd_prepack(const dlp_conv2d_plan *plan, const float *w, void *packed, void *stream)
 {
@@ -250,7 +267,7 @@ dlp_status dlp_conv2d_fwd_prepack(const dlp_conv2d_plan *plan, const float *w, v
 
 static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, const float *w_raw, const float *packed, const float *bias,
                                float *y, float factor, const float *residual, float residual_scale, int post_act, int batch,
-                               int in_h, int in_w, cudaStream_t stream)
+                               int in_h, int in_w, cudaStream_t stream, void *scratch, size_t scratch_bytes)
 {
     const dlp_conv2d_desc &d = plan->d;
     DLP_REQUIRE(x && y, "null tensor");
@@ -314,7 +331,7 @@ static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, cons
 
     if(plan->kind == CK_TC) {
         DLP_REQUIRE(packed != nullptr, "null packed weights");
-        return launch_contraction_tc(p, plan->packed, packed, stream);
+        return launch_contraction_tc(p, plan->packed, packed, stream, scratch, scratch_bytes);
     }
     DLP_REQUIRE(w_raw != nullptr, "null weights");
     return launch_contraction_ffma(p, d.groups, (long long)cin_g * d.height * d.width, (long long)cout_g * plan->k, cout_g, stream);
@@ -336,14 +353,17 @@ dlp_status dlp_conv2d_fwd_enqueue(const dlp_conv2d_plan *plan, const float *x, c
         if(st != DLP_OK) return st;
         packed = static_cast<const float *>(ws);
     }
-    return conv_enqueue(plan, x, w, packed, bias, y, factor, nullptr, 0.0f, DLP_ACT_IDENTITY, batch, in_h, in_w, (cudaStream_t)stream);
+    void *scratch;
+    size_t scratch_bytes;
+    scratch_after(ws, ws_bytes, dlp_conv2d_fwd_packed_bytes(plan), scratch, scratch_bytes);
+    return conv_enqueue(plan, x, w, packed, bias, y, factor, nullptr, 0.0f, DLP_ACT_IDENTITY, batch, in_h, in_w, (cudaStream_t)stream,
+                        scratch, scratch_bytes);
 }
 
 dlp_status dlp_conv2d_fwd_enqueue_packed(const dlp_conv2d_plan *plan, const float *x, const void *packed, const float *bias, float *y,
                                          void *ws, size_t ws_bytes, float factor, const float *residual, float residual_scale,
                                          int post_activation, int batch, int in_h, int in_w, void *stream)
 {
-    (void)ws; (void)ws_bytes;
     DLP_REQUIRE(plan != nullptr, "null plan");
     DLP_REQUIRE(batch >= 0, "negative batch");
     if(batch == 0) return DLP_OK;
@@ -354,7 +374,7 @@ dlp_status dlp_conv2d_fwd_enqueue_packed(const dlp_conv2d_plan *plan, const floa
     const float *pk = takes_packed ? static_cast<const float *>(packed) : nullptr;
     if(residual && plan->kind == CK_DEPTHWISE) return fail(DLP_NOT_IMPLEMENTED, "the depthwise kernel has no fused residual");
     return conv_enqueue(plan, x, raw, pk, bias, y, factor, residual, residual_scale, post_activation, batch, in_h, in_w,
-                        (cudaStream_t)stream);
+                        (cudaStream_t)stream, ws, ws_bytes);
 }
 
 // ---------------------------------------------------------------------------------------------- GEMM
@@ -405,7 +425,9 @@ const char *dlp_gemm_kernel(const dlp_gemm_plan *plan) { return plan ? plan->ker
 size_t dlp_gemm_workspace(const dlp_gemm_plan *plan)
 {
     if(!plan || !plan->use_tc) return 0;
-    return tc_packed_layout(std::max(plan->d.n, 1), std::max(plan->d.k, 1)).bytes();
+    const TcPacked L = tc_packed_layout(std::max(plan->d.n, 1), std::max(plan->d.k, 1));
+    const size_t split = tc_split_scratch_bytes(std::max(plan->d.m, 1), L);
+    return split ? align256(L.bytes()) + split : L.bytes();
 }
 
 dlp_status dlp_gemm_enqueue(const dlp_gemm_plan *plan, int m, int n, int k, const float *a, int lda, const float *b, int ldb, float *c,
@@ -421,7 +443,10 @@ dlp_status dlp_gemm_enqueue(const dlp_gemm_plan *plan, int m, int n, int k, cons
         DLP_REQUIRE(ws != nullptr && ws_bytes >= L.bytes(), "workspace smaller than the packed B operand needs");
         st = tc_prepack(L, b, p.b_col_stride, p.b_k_stride, n, k, static_cast<float *>(ws), 0, (cudaStream_t)stream);
         if(st != DLP_OK) return st;
-        return launch_contraction_tc(p, L, static_cast<const float *>(ws), (cudaStream_t)stream);
+        void *scratch;
+        size_t scratch_bytes;
+        scratch_after(ws, ws_bytes, L.bytes(), scratch, scratch_bytes);
+        return launch_contraction_tc(p, L, static_cast<const float *>(ws), (cudaStream_t)stream, scratch, scratch_bytes);
     }
     return launch_contraction_ffma(p, 1, 0, 0, n, (cudaStream_t)stream);
 }
@@ -459,7 +484,13 @@ dlp_status dlp_ip_fwd_create(const dlp_ip_desc *desc, dlp_ip_plan **out)
 void dlp_ip_fwd_destroy(dlp_ip_plan *plan) { delete plan; }
 const char *dlp_ip_fwd_kernel(const dlp_ip_plan *plan) { return plan ? plan->kernel.c_str() : ""; }
 size_t dlp_ip_fwd_packed_bytes(const dlp_ip_plan *plan) { return plan && plan->use_tc ? plan->packed.bytes() : 0; }
-size_t dlp_ip_fwd_workspace(const dlp_ip_plan *plan) { return dlp_ip_fwd_packed_bytes(plan); }
+size_t dlp_ip_fwd_workspace(const dlp_ip_plan *plan)
+{
+    const size_t packed = dlp_ip_fwd_packed_bytes(plan);
+    if(!plan || !plan->use_tc) return packed;
+    const size_t split = tc_split_scratch_bytes(std::max(plan->d.optimal_batch_size, 1), plan->packed);
+    return split ? align256(packed) + split : packed;
+}
 
 dlp_status dlp_ip_fwd_prepack(const dlp_ip_plan *plan, const float *w, void *packed, void *stream)
 {
@@ -470,7 +501,7 @@ dlp_status dlp_ip_fwd_prepack(const dlp_ip_plan *plan, const float *w, void *pac
 }
 
 static dlp_status ip_enqueue(const dlp_ip_plan *plan, const float *x, const float *w_raw, const float *packed, const float *bias, float *y,
-                             int batch, cudaStream_t stream)
+                             int batch, cudaStream_t stream, void *scratch, size_t scratch_bytes)
 {
     DLP_REQUIRE(batch >= 0, "negative batch");
     if(batch == 0) return DLP_OK;
@@ -487,7 +518,7 @@ static dlp_status ip_enqueue(const dlp_ip_plan *plan, const float *x, const floa
     dlp_status st = gemm_problem(g, batch, plan->d.outputs, plan->d.inputs, x, plan->d.inputs, b_any, plan->d.inputs, y, plan->d.outputs,
                                  bias, 0.0f, p);
     if(st != DLP_OK) return st;
-    if(plan->use_tc) return launch_contraction_tc(p, plan->packed, packed, stream);
+    if(plan->use_tc) return launch_contraction_tc(p, plan->packed, packed, stream, scratch, scratch_bytes);
     return launch_contraction_ffma(p, 1, 0, 0, plan->d.outputs, stream);
 }
 
@@ -503,16 +534,19 @@ dlp_status dlp_ip_fwd_enqueue(const dlp_ip_plan *plan, const float *x, const flo
         if(st != DLP_OK) return st;
         packed = static_cast<const float *>(ws);
     }
-    return ip_enqueue(plan, x, w, packed, bias, y, batch, (cudaStream_t)stream);
+    void *scratch;
+    size_t scratch_bytes;
+    scratch_after(ws, ws_bytes, dlp_ip_fwd_packed_bytes(plan), scratch, scratch_bytes);
+    return ip_enqueue(plan, x, w, packed, bias, y, batch, (cudaStream_t)stream, scratch, scratch_bytes);
 }
 
-dlp_status dlp_ip_fwd_enqueue_packed(const dlp_ip_plan *plan, const float *x, const void *packed, const float *bias, float *y, int batch,
-                                     void *stream)
+dlp_status dlp_ip_fwd_enqueue_packed(const dlp_ip_plan *plan, const float *x, const void *packed, const float *bias, float *y, void *ws,
+                                     size_t ws_bytes, int batch, void *stream)
 {
     DLP_REQUIRE(plan != nullptr, "null plan");
     DLP_REQUIRE(packed != nullptr, "null weights");
     const float *pk = static_cast<const float *>(packed);
-    return ip_enqueue(plan, x, plan->use_tc ? nullptr : pk, plan->use_tc ? pk : nullptr, bias, y, batch, (cudaStream_t)stream);
+    return ip_enqueue(plan, x, plan->use_tc ? nullptr : pk, plan->use_tc ? pk : nullptr, bias, y, batch, (cudaStream_t)stream, ws, ws_bytes);
 }
 
 } // extern "C"

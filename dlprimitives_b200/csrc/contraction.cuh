@@ -20,7 +20,8 @@ enum : int {
 };
 enum : int {
     OUT_NCHW = 0,     // row = (b, pix): y[(b * out_channels_total + col) * out_plane + pix]
-    OUT_ROW_MAJOR = 1 // y[row * ldc + col]
+    OUT_ROW_MAJOR = 1, // y[row * ldc + col]
+    OUT_COL_MAJOR = 2  // y[col * ldc + row]: the scratch layout of split-K partial results
 };
 
 struct KTap {
@@ -88,19 +89,19 @@ __device__ __forceinline__ RowInfo make_row(const Contraction &p, long long row)
         r.iy0 = oy * p.stride_h - p.pad_h;
         r.ix0 = ox * p.stride_w - p.pad_w;
         r.base = (long long)b * p.a_batch_stride + (long long)r.iy0 * p.in_w + r.ix0;
-        r.out = p.out_mode == OUT_NCHW ? (long long)b * p.out_channels_total * p.plane + pix : row * p.ldc;
+        r.out = p.out_mode == OUT_NCHW ? (long long)b * p.out_channels_total * p.plane + pix : (p.out_mode == OUT_COL_MAJOR ? row : row * p.ldc);
     }
     else {
         r.iy0 = r.ix0 = 0;
         r.base = row * p.a_row_stride;
-        r.out = row * p.ldc;
+        r.out = p.out_mode == OUT_COL_MAJOR ? row : row * p.ldc;
     }
     return r;
 }
 
 __device__ __forceinline__ long long out_index(const Contraction &p, const RowInfo &r, int col)
 {
-    return p.out_mode == OUT_NCHW ? r.out + (long long)col * p.plane : r.out + col;
+    return p.out_mode == OUT_NCHW ? r.out + (long long)col * p.plane : (p.out_mode == OUT_COL_MAJOR ? r.out + (long long)col * p.ldc : r.out + col);
 }
 
 __device__ __forceinline__ float finish_output(const Contraction &p, const RowInfo &r, long long row, int col, float acc)
@@ -131,7 +132,11 @@ TcPacked tc_packed_layout(int cols, int k);
 // taps > 0 packs in the A_TAPBLOCK order: packed k = ((channel block * taps + tap) * 32 + channel in block)
 dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
                       float *packed, int taps, cudaStream_t stream);
-dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream);
+// Scratch that lets the launcher split K when the problem has too few tiles for the GPU (0: it would not split).
+size_t tc_split_scratch_bytes(long long rows, const TcPacked &L);
+// scratch may be null or short; the launcher then does not split.
+dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream, void *scratch = nullptr,
+                                 size_t scratch_bytes = 0);
 
 // Winograd F(2x2, 3x3), stride 1, padding 1 (winograd.cu).  u: the transformed filters, winograd_packed_bytes() long.
 size_t winograd_packed_bytes(int cin, int cout);

@@ -287,6 +287,15 @@ __device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const
 __device__ long long g_trace[64 * 16];
 #endif
 
+// work item -> (tile, part of K)
+__device__ __forceinline__ void decode_item(long long item, int splits, long long &tile, int &part)
+{
+    if(splits == 1) { tile = item; part = 0; return; }
+    const unsigned t = unsigned(item) / unsigned(splits);      // items fit 32 bits whenever K is split (few tiles)
+    tile = t;
+    part = int(unsigned(item) - t * unsigned(splits));
+}
+
 // Position of a loader in the CTA's sequence of k-blocks (the sequence runs on across tiles).
 struct Cursor {
     long long tile;
@@ -294,12 +303,17 @@ struct Cursor {
     uint32_t it;
 };
 
+// Split K: when a problem has too few tiles to fill the GPU the launcher cuts K into `splits` equal parts.
+// The kernel then sees num_tiles = tiles * splits work items of kblocks = (all k-blocks) / splits each;
+// item = tile * splits + part.  Part s reads its own k-blocks of A and B and writes its partial result
+// raw to y + s * split_stride (the launcher points y at scratch); a second kernel adds the parts in order.
+//
 // BN: column tile.  MODE: how the loaders address A (A_GATHER / A_STRIDED / A_TAPBLOCK); a template
 // parameter so that each kernel carries one loader only -- the roles share a small instruction cache.
 template<int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p, int kblocks, int n_tiles,
-                          long long num_tiles, int *status, int diag, long long *trace)
+                          long long num_tiles, int splits, long long split_stride, int *status, int diag, long long *trace)
 {
 #ifdef DLP_TC_DIAGNOSTICS
     // optional timeline of CTA 0: trace[k-block or chunk][slot] = SM clock at a few points of each role
@@ -353,10 +367,13 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         if(lane == 0) {
             uint32_t it = 0;
             bool live = true;
-            for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
+            for(long long item = blockIdx.x; item < num_tiles && live; item += gridDim.x) {
                 // the packed operand holds the stages in the order (column tile, k-block), each one the exact
                 // shared-memory image of its hi and lo tiles
-                const float *src = packed + (long long)(tile % n_tiles) * kblocks * (B_STAGE_BYTES / 4);
+                long long tile;
+                int part;
+                decode_item(item, splits, tile, part);
+                const float *src = packed + ((long long)(tile % n_tiles) * splits + part) * kblocks * (B_STAGE_BYTES / 4);
                 for(int kb = 0; kb < kblocks; kb++, it++) {
                     const int s = it % STAGES;
                     if(!mbar_wait(&sh->empty[s >> 1], ((it / STAGES) & 1) ^ 1, sh, status, ST_TMA_EMPTY)) { live = false; break; }
@@ -460,18 +477,21 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         const float2 clamp = act_clamp(p.act), post_clamp = act_clamp(p.post_act);
         const bool epi_fast = act_is_clamp(p.act) && act_is_clamp(p.post_act) && p.bias_mode != DLP_GEMM_BIAS_M && p.beta == 0.0f;
         bool live = true;
-        for(long long tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x) {
+        for(long long item = blockIdx.x; item < num_tiles && live; item += gridDim.x) {
+            long long tile;
+            int part;
+            decode_item(item, splits, tile, part);
             const int n0 = int(tile % n_tiles) * BN;
             const long long row = (tile / n_tiles) * BM + row_in_tile;
             const RowInfo r = make_row(p, row);
-            const long long col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : 1ll;
+            const long long col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : (p.out_mode == OUT_COL_MAJOR ? p.ldc : 1ll);
             // The tile is handled 32 columns at a time: two tensor-memory loads under one wait; on the last
             // chunk the residual operand of the same columns is fetched under that wait as well.
             constexpr int G = BN >= 32 ? 32 : 16;
             constexpr int GROUPS = BN / G;
             const bool fast = epi_fast && r.valid && n0 + BN <= p.cols && !TC_DIAG(DIAG_NO_STORES);
             const bool with_res = fast && p.residual != nullptr;
-            float *y_row = p.y + r.out + (long long)n0 * col_stride;
+            float *y_row = p.y + part * split_stride + r.out + (long long)n0 * col_stride;
             const float *res_row = with_res ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
             for(int c = 0; c < chunks_per_tile; c++, chunk++) {
                 const uint32_t buf = chunk & 1;
@@ -532,7 +552,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                         if(r.valid && !TC_DIAG(DIAG_NO_STORES)) {
                             #pragma unroll 1
                             for(int j = 0; j < G; j++)
-                                if(col0 + j < p.cols) p.y[out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, sg[j * BM]);
+                                if(col0 + j < p.cols) p.y[part * split_stride + out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, sg[j * BM]);
                         }
                     }
                     if(quad == 0 && lane == 0) TC_TRACE(11, chunk * GROUPS + g);
@@ -545,7 +565,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         const int quad = warp & 3;                       // tensor-memory lanes this warp may touch
         const int group = (warp - WARP_LOAD0) >> 2;      // this warp handles k-blocks with (it & 1) == group
         const int row_in_tile = quad * 32 + lane;
-        long long loaded_tile = -1;
+        long long loaded_tile = -1, loaded_row_tile = 0;      // Cursor::tile counts work items
+        int loaded_part = 0;
         RowInfo r;
         r.valid = false; r.base = 0; r.iy0 = r.ix0 = 0; r.out = 0;
 
@@ -564,7 +585,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         auto issue_loads = [&](const Cursor &c, float (&buf)[BK]) {
             if(c.tile != loaded_tile) {
                 loaded_tile = c.tile;
-                r = make_row(p, (c.tile / n_tiles) * BM + row_in_tile);
+                decode_item(c.tile, splits, loaded_row_tile, loaded_part);
+                r = make_row(p, (loaded_row_tile / n_tiles) * BM + row_in_tile);
                 if(TC_DIAG(DIAG_NO_A_LOADS)) r.valid = false;
                 tap_mask = 0;
                 if(MODE != A_STRIDED && r.valid)
@@ -574,7 +596,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                         if(unsigned(iy) < unsigned(p.in_h) && unsigned(ix) < unsigned(p.in_w)) tap_mask |= 1ull << t;
                     }
             }
-            const int k0 = c.kb * BK;
+            const int kb_all = loaded_part * kblocks + c.kb;       // k-block within the whole of K
+            const int k0 = kb_all * BK;
             if(MODE == A_STRIDED) {
                 const float *src = p.a + r.base + (long long)k0 * p.a_k_stride;
                 if(row_vec && r.valid && k0 + BK <= p.k) {
@@ -599,7 +622,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 }
             }
             else if(MODE == A_TAPBLOCK) {
-                const int cb = c.kb / p.num_taps, t = c.kb - cb * p.num_taps;
+                const int cb = kb_all / p.num_taps, t = kb_all - cb * p.num_taps;
                 const int d = __ldg(p.tap_dydx + t);
                 const float *src = p.a + r.base + (long long)(cb * BK) * p.a_k_stride + (d >> 16) * p.in_w + (d & 0xffff);
                 if((tap_mask >> t) & 1ull) {
@@ -739,6 +762,22 @@ __global__ void prepack_kernel(const float *__restrict__ b, long long col_stride
     }
 }
 
+// Second step of a split-K contraction: add the partial results in a fixed order (so the sum does not
+// depend on timing) and apply the epilogue.  Partials are column-major [part][col][rows_pad].
+__global__ void split_finish_kernel(const Contraction p, const float *__restrict__ partial, int splits, long long split_stride, long long rows_pad)
+{
+    const long long total = p.rows * p.cols;
+    for(long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const int col = int(idx / p.rows);
+        const long long row = idx - (long long)col * p.rows;
+        const float *src = partial + (long long)col * rows_pad + row;
+        float acc = __ldg(src);
+        for(int s = 1; s < splits; s++) acc += __ldg(src + s * split_stride);
+        const RowInfo r = make_row(p, row);
+        p.y[out_index(p, r, col)] = finish_output(p, r, row, col, acc);
+    }
+}
+
 } // namespace tc
 
 // ---------------------------------------------------------------------------------------------- host
@@ -764,8 +803,20 @@ dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride,
 }
 
 namespace {
+// How many parts to cut K into: only when the tiles fill less than half of the SMs, in equal parts of
+// whole partial-accumulator chunks, as many as there are idle SMs for.
+int choose_splits(long long rows, const TcPacked &L)
+{
+    const long long tiles = ceil_div<long long>(rows, tc::BM) * (L.n_pad / L.bn);
+    const int kb = L.k_pad / tc::BK;
+    if(tiles <= 0 || tiles * 2 > sm_count() || kb < 2 * tc::CHUNK_KB) return 1;
+    for(int s = int(std::min<long long>(sm_count() / tiles, kb / tc::CHUNK_KB)); s >= 2; s--)
+        if(kb % s == 0 && (kb / s) % tc::CHUNK_KB == 0) return s;
+    return 1;
+}
+
 template<int BN, int MODE>
-dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream)
+dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream, int splits, long long split_stride)
 {
     const int smem = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int(sizeof(tc::Shared));
     static bool configured = false;   // per instantiation; the attribute is per function, set once per process
@@ -775,7 +826,7 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packe
     }
     const long long m_tiles = ceil_div<long long>(p.rows, tc::BM);
     const int n_tiles = L.n_pad / BN;
-    const long long num_tiles = m_tiles * n_tiles;
+    const long long num_tiles = m_tiles * n_tiles * splits;     // work items
     const int grid = int(std::min<long long>(num_tiles, sm_count()));
     int diag = 0;
     long long *trace = nullptr;
@@ -791,8 +842,8 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packe
 #endif
     int *status = device_status_word();
     if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
-    tc::contraction_tf32x3_kernel<BN, MODE><<<grid, tc::NUM_THREADS, smem, stream>>>(packed, p, L.k_pad / tc::BK, n_tiles, num_tiles,
-                                                                              status, diag, trace);
+    tc::contraction_tf32x3_kernel<BN, MODE><<<grid, tc::NUM_THREADS, smem, stream>>>(packed, p, L.k_pad / tc::BK / splits, n_tiles, num_tiles,
+                                                                                     splits, split_stride, status, diag, trace);
     DLP_LAUNCH_OK("contraction_tf32x3_kernel");
 #ifdef DLP_TC_DIAGNOSTICS
     if(trace) {
@@ -812,22 +863,53 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packe
 }
 } // namespace
 
-dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream)
+size_t tc_split_scratch_bytes(long long rows, const TcPacked &L)
+{
+    const int s = choose_splits(rows, L);
+    return s > 1 ? size_t(s) * size_t(ceil_div<long long>(rows, tc::BM) * tc::BM) * L.n_pad * sizeof(float) : 0;
+}
+
+dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream, void *scratch,
+                                 size_t scratch_bytes)
 {
     if(p.rows <= 0 || p.cols <= 0) return DLP_OK;
     if(reinterpret_cast<uintptr_t>(packed) % 16 != 0) return fail(DLP_INVALID_ARGUMENT, "packed weights must be 16-byte aligned");
-    switch(L.bn * 4 + p.a_mode) {
-    case 32 * 4 + A_GATHER: return launch_bn<32, A_GATHER>(p, L, packed, stream);
-    case 32 * 4 + A_STRIDED: return launch_bn<32, A_STRIDED>(p, L, packed, stream);
-    case 32 * 4 + A_TAPBLOCK: return launch_bn<32, A_TAPBLOCK>(p, L, packed, stream);
-    case 64 * 4 + A_GATHER: return launch_bn<64, A_GATHER>(p, L, packed, stream);
-    case 64 * 4 + A_STRIDED: return launch_bn<64, A_STRIDED>(p, L, packed, stream);
-    case 64 * 4 + A_TAPBLOCK: return launch_bn<64, A_TAPBLOCK>(p, L, packed, stream);
-    case 128 * 4 + A_GATHER: return launch_bn<128, A_GATHER>(p, L, packed, stream);
-    case 128 * 4 + A_STRIDED: return launch_bn<128, A_STRIDED>(p, L, packed, stream);
-    case 128 * 4 + A_TAPBLOCK: return launch_bn<128, A_TAPBLOCK>(p, L, packed, stream);
+    int splits = choose_splits(p.rows, L);
+    const long long rows_pad = ceil_div<long long>(p.rows, tc::BM) * tc::BM;
+    const long long split_stride = rows_pad * L.n_pad;
+    if(splits > 1 && (scratch == nullptr || scratch_bytes < size_t(splits) * split_stride * sizeof(float))) splits = 1;
+    Contraction q = p;
+    if(splits > 1) {
+        // the parts write raw partial sums to the scratch; the epilogue runs in the finishing kernel
+        q.y = static_cast<float *>(scratch);
+        q.out_mode = OUT_COL_MAJOR;
+        q.ldc = rows_pad;
+        q.bias = nullptr;
+        q.bias_mode = DLP_GEMM_NO_BIAS;
+        q.act = DLP_ACT_IDENTITY;
+        q.post_act = DLP_ACT_IDENTITY;
+        q.beta = 0.0f;
+        q.residual = nullptr;
     }
-    return fail(DLP_INVALID_ARGUMENT, "unsupported column tile");
+    dlp_status st = DLP_INVALID_ARGUMENT;
+    switch(L.bn * 4 + p.a_mode) {
+    case 32 * 4 + A_GATHER: st = launch_bn<32, A_GATHER>(q, L, packed, stream, splits, split_stride); break;
+    case 32 * 4 + A_STRIDED: st = launch_bn<32, A_STRIDED>(q, L, packed, stream, splits, split_stride); break;
+    case 32 * 4 + A_TAPBLOCK: st = launch_bn<32, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride); break;
+    case 64 * 4 + A_GATHER: st = launch_bn<64, A_GATHER>(q, L, packed, stream, splits, split_stride); break;
+    case 64 * 4 + A_STRIDED: st = launch_bn<64, A_STRIDED>(q, L, packed, stream, splits, split_stride); break;
+    case 64 * 4 + A_TAPBLOCK: st = launch_bn<64, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride); break;
+    case 128 * 4 + A_GATHER: st = launch_bn<128, A_GATHER>(q, L, packed, stream, splits, split_stride); break;
+    case 128 * 4 + A_STRIDED: st = launch_bn<128, A_STRIDED>(q, L, packed, stream, splits, split_stride); break;
+    case 128 * 4 + A_TAPBLOCK: st = launch_bn<128, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride); break;
+    default: return fail(DLP_INVALID_ARGUMENT, "unsupported column tile");
+    }
+    if(st != DLP_OK || splits == 1) return st;
+    const long long total = p.rows * p.cols;
+    const int blocks = int(std::min<long long>(ceil_div<long long>(total, 256), 16 * sm_count()));
+    tc::split_finish_kernel<<<blocks, 256, 0, stream>>>(p, static_cast<const float *>(scratch), splits, split_stride, rows_pad);
+    DLP_LAUNCH_OK("split_finish_kernel");
+    return DLP_OK;
 }
 
 } // namespace dlp

@@ -72,12 +72,14 @@ public:
         status_check(dlp_conv2d_fwd_prepack(plan_, w.device_data<float>(), packed.device_ptr(), e.stream_handle()));
     }
     void enqueue_packed(Tensor &x, Tensor &packed, Tensor *bias, Tensor &y, Tensor *residual, float residual_scale,
-                        StandardActivations post_activation, ExecutionContext const &e) override
+                        StandardActivations post_activation, Tensor *ws, ExecutionContext const &e) override
     {
         check(x, y, bias);
         if(residual) DLPRIM_CHECK(residual->shape() == y.shape());
+        const size_t ws_bytes = ws ? ws->memory_size() : 0;
         status_check(dlp_conv2d_fwd_enqueue_packed(plan_, x.device_data<float>(), packed.device_ptr(),
-                                                   bias ? bias->device_data<float>() : nullptr, y.device_data<float>(), nullptr, 0, 0.0f,
+                                                   bias ? bias->device_data<float>() : nullptr, y.device_data<float>(),
+                                                   ws_bytes ? ws->device_ptr() : nullptr, ws_bytes, 0.0f,
                                                    residual ? residual->device_data<float>() : nullptr, residual_scale,
                                                    int(post_activation), int(x.shape()[0]), int(x.shape()[2]), int(x.shape()[3]),
                                                    e.stream_handle()));
@@ -132,7 +134,8 @@ public:
     {
         check(x, y, bias);
         status_check(dlp_ip_fwd_enqueue_packed(plan_, x.device_data<float>(), packed.device_ptr(), bias ? bias->device_data<float>() : nullptr,
-                                               y.device_data<float>(), int(x.shape()[0]), e.stream_handle()));
+                                               y.device_data<float>(), ws_bytes_ ? ws_.device_ptr() : nullptr, ws_bytes_, int(x.shape()[0]),
+                                               e.stream_handle()));
     }
 private:
     void check(Tensor &x, Tensor &y, Tensor *bias)

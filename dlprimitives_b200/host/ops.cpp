@@ -111,7 +111,7 @@ void Convolution2D::forward(std::vector<Tensor> &in, std::vector<Tensor> &out, s
     DLPRIM_CHECK(conv_);
     if(cache_packed_ && conv_->packed_weights_size() > 0) {
         ensure_packed(parameters[0], ectx);
-        conv_->enqueue_packed(in[0], packed_, bias, out[0], nullptr, 0.0f, StandardActivations::identity, ectx);
+        conv_->enqueue_packed(in[0], packed_, bias, out[0], nullptr, 0.0f, StandardActivations::identity, &ws, ectx);
     }
     else
         conv_->enqueue(in[0], parameters[0], bias, out[0], ws, 0.0f, ectx);
@@ -120,17 +120,16 @@ void Convolution2D::forward(std::vector<Tensor> &in, std::vector<Tensor> &out, s
 void Convolution2D::forward_fused(Tensor &x, Tensor &y, std::vector<Tensor> &parameters, Tensor &ws, Tensor &residual, float residual_scale,
                                   StandardActivations post_activation, ExecutionContext const &ectx)
 {
-    (void)ws;
     DLPRIM_CHECK(conv_);
     DLPRIM_CHECK(y.shape() == get_output_shape(x.shape()));
     DLPRIM_CHECK(parameters.size() == (1u + unsigned(config_.bias)));
     Tensor *bias = config_.bias ? &parameters[1] : nullptr;
     if(conv_->packed_weights_size() > 0) {
         ensure_packed(parameters[0], ectx);
-        conv_->enqueue_packed(x, packed_, bias, y, &residual, residual_scale, post_activation, ectx);
+        conv_->enqueue_packed(x, packed_, bias, y, &residual, residual_scale, post_activation, &ws, ectx);
     }
     else
-        conv_->enqueue_packed(x, parameters[0], bias, y, &residual, residual_scale, post_activation, ectx);
+        conv_->enqueue_packed(x, parameters[0], bias, y, &residual, residual_scale, post_activation, &ws, ectx);
 }
 
 // ================================================================================ InnerProduct

@@ -95,7 +95,10 @@ DLP_API void dlp_conv2d_fwd_destroy(dlp_conv2d_plan *plan);
 DLP_API const char *dlp_conv2d_fwd_algo(const dlp_conv2d_plan *plan);
 /* Name of the kernel variant behind the plan, e.g. "igemm_tf32x3_bn128". */
 DLP_API const char *dlp_conv2d_fwd_kernel(const dlp_conv2d_plan *plan);
-/* Conv2DBase::workspace(): bytes of scratch enqueue needs for the planned batch. */
+/* Conv2DBase::workspace(): bytes of scratch enqueue needs for the planned batch: the packed weights, plus,
+ * for problems with too few output tiles to fill the GPU, room for partial sums over parts of K (the
+ * results are added in a fixed order, so they do not depend on timing).  enqueue_packed uses a workspace
+ * only for the latter; a short or missing one just turns the split off. */
 DLP_API size_t dlp_conv2d_fwd_workspace(const dlp_conv2d_plan *plan);
 /* Bytes of the pre-packed form of the weights (0 when the kernel reads raw weights). */
 DLP_API size_t dlp_conv2d_fwd_packed_bytes(const dlp_conv2d_plan *plan);
@@ -176,8 +179,9 @@ DLP_API size_t dlp_ip_fwd_packed_bytes(const dlp_ip_plan *plan);
 DLP_API dlp_status dlp_ip_fwd_prepack(const dlp_ip_plan *plan, const float *w, void *packed, void *stream);
 DLP_API dlp_status dlp_ip_fwd_enqueue(const dlp_ip_plan *plan, const float *x, const float *w, const float *bias, float *y,
                                       void *ws, size_t ws_bytes, int batch, void *stream);
+/* ws: optional scratch (dlp_ip_fwd_workspace() bytes at most are used) that lets a small batch use the whole GPU. */
 DLP_API dlp_status dlp_ip_fwd_enqueue_packed(const dlp_ip_plan *plan, const float *x, const void *packed, const float *bias,
-                                             float *y, int batch, void *stream);
+                                             float *y, void *ws, size_t ws_bytes, int batch, void *stream);
 
 /* InnerProduct forward without any device allocation and without a caller workspace.
  * It has no counterpart in the reference library.  It exists for callers that are not allowed to

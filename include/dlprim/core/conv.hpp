@@ -36,8 +36,10 @@ namespace core {
         ///  y = post_act( act(conv(x, w) + bias) + residual_scale * residual ).
         virtual size_t packed_weights_size() const = 0;
         virtual void pack_weights(Tensor &w, Tensor &packed, ExecutionContext const &e) = 0;
+        ///  ws: optional scratch of workspace() bytes; with it a problem of few output tiles is cut along K
+        ///  so that it still uses the whole GPU (null: no cut).
         virtual void enqueue_packed(Tensor &x, Tensor &packed, Tensor *bias, Tensor &y, Tensor *residual, float residual_scale,
-                                    StandardActivations post_activation, ExecutionContext const &e) = 0;
+                                    StandardActivations post_activation, Tensor *ws, ExecutionContext const &e) = 0;
         /// name of the kernel variant behind this object
         virtual char const *kernel_name() const = 0;
 

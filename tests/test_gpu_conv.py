@@ -270,3 +270,39 @@ def test_winograd_config_shapes(cin, hw, cout, batch):
     plan.enqueue_packed(xd, packed, bd, y2, residual=to_dev(res), residual_scale=1.0, post_activation="relu")
     assert rel_err(y2.cpu().numpy(), np.maximum(want + res, 0.0)) <= REL_TOL
     assert capi.device_status() == 0
+
+
+def test_split_k_small_batch_matches_checker_and_is_deterministic():
+    """A problem with few output tiles (layer-4 shapes at a small batch) is cut along K when the caller
+    provides the workspace: same result as the checker, run-to-run identical, and within rounding of the
+    uncut kernel (a different but fixed summation order)."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    ob.set_threads(16)
+    rng = np.random.default_rng(404)
+    for cin, cout, k, pad in ((512, 512, 3, 1), (1024, 512, 1, 0)):
+        batch, hw = 4, 7
+        x = rng.standard_normal((batch, cin, hw, hw), dtype=np.float32)
+        w = kaiming(rng, (cout, cin, k, k))
+        b = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+        res = rng.standard_normal((batch, cout, hw, hw), dtype=np.float32)
+        plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, stride=1, pad=pad, batch=batch, height=hw, width=hw,
+                                  bias=True, activation="identity")
+        assert plan.workspace() > plan.packed_bytes()        # room for the partial sums is part of the workspace
+        xd, wd, bd, rd = to_dev(x), to_dev(w), to_dev(b), to_dev(res)
+        packed = plan.prepack(wd)
+        ws = torch.empty(plan.workspace(), dtype=torch.uint8, device=DEV)
+        want = np.maximum(ob.conv2d(x, w, b, stride=1, pad=pad) + res, 0.0)
+        outs = []
+        for use_ws in (ws, ws, None):
+            y = torch.full(plan.output_shape(batch), float("nan"), device=DEV)
+            plan.enqueue_packed(xd, packed, bd, y, residual=rd, post_activation="relu", ws=use_ws)
+            torch.cuda.synchronize()
+            outs.append(y.cpu().numpy())
+        assert rel_err(outs[0], want) <= REL_TOL and rel_err(outs[2], want) <= REL_TOL
+        assert np.array_equal(outs[0], outs[1])
+        # the plain call packs into the same workspace and cuts K as well
+        y = torch.full(plan.output_shape(batch), float("nan"), device=DEV)
+        plan.enqueue(xd, wd, bd, y, ws)
+        assert rel_err(y.cpu().numpy(), ob.conv2d(x, w, b, stride=1, pad=pad)) <= REL_TOL
+    assert capi.device_status() == 0
