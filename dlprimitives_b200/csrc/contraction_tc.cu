@@ -803,16 +803,24 @@ dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride,
 }
 
 namespace {
-// How many parts to cut K into: only when the tiles fill less than half of the SMs, in equal parts of
-// whole partial-accumulator chunks, as many as there are idle SMs for.
+// How many equal parts to cut K into.  Time is counted in k-block periods: a CTA works through
+// ceil(items / SMs) work items of (k-blocks per part + a fixed cost for pipeline fill and epilogue) each,
+// and a split run pays for the finishing kernel.  K is cut only when that model gains a tenth or more.
 int choose_splits(long long rows, const TcPacked &L)
 {
     const long long tiles = ceil_div<long long>(rows, tc::BM) * (L.n_pad / L.bn);
-    const int kb = L.k_pad / tc::BK;
-    if(tiles <= 0 || tiles * 2 > sm_count() || kb < 2 * tc::CHUNK_KB) return 1;
-    for(int s = int(std::min<long long>(sm_count() / tiles, kb / tc::CHUNK_KB)); s >= 2; s--)
-        if(kb % s == 0 && (kb / s) % tc::CHUNK_KB == 0) return s;
-    return 1;
+    const int kb = L.k_pad / tc::BK, sms = sm_count();
+    if(tiles <= 0 || tiles > 4 * sms || kb < 8) return 1;
+    const double item_fixed = 6.0, finish = 10.0;
+    const double uncut = double(ceil_div<long long>(tiles, sms)) * (kb + item_fixed);
+    int best = 1;
+    double best_cost = 0.9 * uncut;
+    for(int s = 2; s <= 32 && kb / s >= 4; s++) {
+        if(kb % s != 0) continue;
+        const double cost = double(ceil_div<long long>(tiles * s, sms)) * (kb / s + item_fixed) + finish;
+        if(cost < best_cost) { best = s; best_cost = cost; }
+    }
+    return best;
 }
 
 template<int BN, int MODE>

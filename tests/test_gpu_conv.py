@@ -110,11 +110,12 @@ def test_config_shapes_full_size(cfg):
     want = ob.conv2d(x[sel], w, b, stride=stride, pad=pad, groups=groups, activation=act)
     err = rel_err(got[sel], want)
     assert err <= REL_TOL, (plan.kernel(), err)
-    # a cheap whole-batch property: every image of the batch gives the same result as when it runs alone
+    # a cheap whole-batch property: every image of the batch gives the same result as when it runs alone,
+    # up to the order of the fp32 sum over K (a batch with few output tiles is cut along K)
     y1 = torch.empty(plan.output_shape(1), device=DEV)
     for i in (0, N - 1):
         plan.enqueue(xd[i:i + 1].contiguous(), wd, bd, y1, ws)
-        assert torch.equal(y1[0], y[i])
+        assert rel_err(y1[0].cpu().numpy(), y[i].cpu().numpy()) <= 2e-6
 
 
 def test_depthwise_mobilenet_rows():

@@ -37,7 +37,9 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row():
         g, r = got.cpu().numpy(), want.cpu().numpy()
         assert not np.isnan(g).any()
         assert rel_err(g, r) <= REL_TOL, (call, rel_err(g, r))
-        assert np.array_equal(g, r)                          # same kernels, same data: in fact identical
+        # the same kernel on the same data; the workspace call may cut K into parts (it has the scratch for
+        # the partial sums, this entry point does not), so the two agree to the rounding of the fp32 sum
+        assert rel_err(g, r) <= 2e-6
     assert capi.device_status() == 0
 
 
