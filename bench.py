@@ -315,10 +315,10 @@ def run_gpu_arm(args, rank, world, local_rank):
     achieved = tc_flops / tc_ms if tc_ms > 0 else 0.0      # GFLOP / ms = TFLOP/s
     # DRAM bytes per contraction launch, from one ncu pass over a forward at 256 images on one GPU
     # (profiles/contraction_tf32x3_forward_dram_traffic.md); not measured for other per-GPU batches
-    traffic = {"value": 486.0e6, "unit": "bytes per launch (average of the forward's launches)", "algorithmic": 1e6 * sum(r["mbytes"] for r in tc) / max(len(tc), 1),
-               "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum"} if local_batch == 256 else None
+    traffic = 486.0e6 if local_batch == 256 else None
     roofline = {"bound": "tensor", "kernel": "contraction_tf32x3_kernel", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
-                "frac": achieved / tensor_peak, "traffic": traffic, "launches": len(tc), "avg_launch_ms": tc_ms / max(len(tc), 1),
+                "frac": achieved / tensor_peak, "traffic": traffic, "traffic_unit": "DRAM bytes per launch, average over the forward's launches",
+                "algorithmic_bytes_per_launch": 1e6 * sum(r["mbytes"] for r in tc) / max(len(tc), 1), "launches": len(tc), "avg_launch_ms": tc_ms / max(len(tc), 1),
                 "peak_source": "%s bf16 sustained %.1f TFLOP/s / 2 (TF32) / 3 (products per term)" % (peaks["source"], peaks["bf16_tflops_sustained"]),
                 "share_of_forward": tc_ms / sum(r["ms"] for r in rows)}
 
