@@ -183,7 +183,9 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
         // reference (src/core/conv.cpp:719-727)
         plan->algo = "gemm";
         // the tensor-core loader keeps one validity bit per kernel tap in a 64-bit word
-        const bool tc_ok = d.groups == 1 && d.math_mode != DLP_MATH_FP32_FFMA && d.kernel[0] * d.kernel[1] <= MAX_TAPS;
+        // (and one validity bit per kernel row and column in 32-bit words, bit 31 standing for "never")
+        const bool tc_ok = d.groups == 1 && d.math_mode != DLP_MATH_FP32_FFMA && d.kernel[0] * d.kernel[1] <= MAX_TAPS &&
+                           d.kernel[0] <= 30 && d.kernel[1] <= 30;
         if(d.math_mode == DLP_MATH_TF32X3 && !tc_ok)
             return fail(DLP_NOT_IMPLEMENTED, "the tensor-core kernel handles groups == 1 and kernels of at most 63 taps");
         plan->kind = tc_ok ? CK_TC : CK_FFMA;
@@ -210,7 +212,7 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
                     for(int kx = 0; kx < d.kernel[1]; kx++, idx++) {
                         const int dy = ky * d.dilate[0], dx = kx * d.dilate[1];
                         tab[idx].offset = (c * d.height + dy) * d.width + dx;
-                        tab[idx].tap = plan->kind == CK_TC ? ky * d.kernel[1] + kx : std::min(ky * d.kernel[1] + kx, plan->num_taps - 1);
+                        tab[idx].tap = plan->kind == CK_TC ? (ky << 8) | kx : std::min(ky * d.kernel[1] + kx, plan->num_taps - 1);
                         taps[ky * d.kernel[1] + kx] = (dy << 16) | dx;
                     }
             for(; idx < k_pad; idx++) { tab[idx].offset = 0; tab[idx].tap = TAP_PADDING; }
@@ -314,6 +316,8 @@ static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, cons
         p.ktab = plan->ktab;
         p.tap_dydx = plan->tap_dydx;
         p.num_taps = plan->num_taps;
+        p.kh = d.kernel[0]; p.kw = d.kernel[1];
+        p.dil_h = d.dilate[0]; p.dil_w = d.dilate[1];
     }
     p.b = w_raw;
     p.b_col_stride = plan->k;

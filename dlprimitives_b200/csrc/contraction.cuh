@@ -26,9 +26,10 @@ enum : int {
 
 struct KTap {
     int offset;  // element offset of reduction index k from the row's base address: c*H*W + dy*W + dx
-    int tap;     // which kernel tap (ky*KW + kx) it belongs to; TAP_PADDING for the zero padding beyond K
+    int tap;     // FFMA kernel: the kernel tap ky*KW + kx.  Tensor-core kernel: (ky << 8) | kx, and
+                 // TAP_PADDING for the zero padding beyond K (a kernel row that never exists)
 };
-constexpr int TAP_PADDING = 63;
+constexpr int TAP_PADDING = 31 << 8;
 constexpr int MAX_TAPS = 63;     // kernels with more taps than bits in the per-pixel validity mask use the FFMA path
 
 struct Contraction {
@@ -50,6 +51,7 @@ struct Contraction {
     const KTap *ktab;    // k_pad entries
     const int *tap_dydx; // num_taps entries: (dy << 16) | dx displacement of each kernel tap (dilation included)
     int num_taps;
+    int kh, kw, dil_h, dil_w;   // kernel size and dilation (tensor-core loaders: which taps fall inside the image)
     // B side, raw form: B(col, k) = b[col * b_col_stride + k * b_k_stride]
     const float *b;
     long long b_col_stride, b_k_stride;

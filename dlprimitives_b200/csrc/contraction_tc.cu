@@ -313,7 +313,8 @@ struct Cursor {
 template<int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p, int kblocks, int n_tiles,
-                          long long num_tiles, int splits, long long split_stride, int *status, int diag, long long *trace)
+                          long long num_tiles, int splits, long long split_stride, int ktab_smem_entries, int *status, int diag,
+                          long long *trace)
 {
 #ifdef DLP_TC_DIAGNOSTICS
     // optional timeline of CTA 0: trace[k-block or chunk][slot] = SM clock at a few points of each role
@@ -334,6 +335,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
     unsigned char *b_ring = smem;
     float *sums = reinterpret_cast<float *>(smem + STAGES * B_STAGE_BYTES);   // [BN][BM]: column-major, a thread owns a row
     Shared *sh = reinterpret_cast<Shared *>(smem + STAGES * B_STAGE_BYTES + BN * BM * 4);
+    // gather mode: a copy of the (k -> offset, tap) table when it is small enough (ktab_smem_entries > 0)
+    int4 *ktab_s = reinterpret_cast<int4 *>(smem + STAGES * B_STAGE_BYTES + BN * BM * 4 + ((sizeof(Shared) + 15) & ~size_t(15)));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -357,6 +360,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if(MODE == A_GATHER)
+        for(int i = threadIdx.x; i < ktab_smem_entries / 2; i += NUM_THREADS) ktab_s[i] = __ldg(reinterpret_cast<const int4 *>(p.ktab) + i);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -581,21 +586,23 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         // Per tile the thread works out once whether its row exists and, for a convolution, which of the
         // kernel's taps fall inside the image for its pixel (a bit per tap), so the per-element work is
         // a table entry, a bit test and the load.
-        unsigned long long tap_mask = 0;
+        unsigned row_mask = 0, col_mask = 0;     // bit ky / kx: that kernel row / column falls inside the image for this pixel
         auto issue_loads = [&](const Cursor &c, float (&buf)[BK]) {
             if(c.tile != loaded_tile) {
                 loaded_tile = c.tile;
                 decode_item(c.tile, splits, loaded_row_tile, loaded_part);
                 r = make_row(p, (loaded_row_tile / n_tiles) * BM + row_in_tile);
                 if(TC_DIAG(DIAG_NO_A_LOADS)) r.valid = false;
-                tap_mask = 0;
-                if(MODE != A_STRIDED && r.valid)
-                    for(int t = 0; t < p.num_taps; t++) {
-                        const int d = __ldg(p.tap_dydx + t);
-                        const int iy = r.iy0 + (d >> 16), ix = r.ix0 + (d & 0xffff);
-                        if(unsigned(iy) < unsigned(p.in_h) && unsigned(ix) < unsigned(p.in_w)) tap_mask |= 1ull << t;
-                    }
+                row_mask = col_mask = 0;
+                if(MODE == A_GATHER && r.valid) {
+                    for(int ky = 0; ky < p.kh; ky++)
+                        if(unsigned(r.iy0 + ky * p.dil_h) < unsigned(p.in_h)) row_mask |= 1u << ky;
+                    for(int kx = 0; kx < p.kw; kx++)
+                        if(unsigned(r.ix0 + kx * p.dil_w) < unsigned(p.in_w)) col_mask |= 1u << kx;
+                }
             }
+            // table entry (ky << 8) | kx -> is that tap inside the image for this thread's pixel
+            auto tap_inside = [&](int tap) { return ((row_mask >> (tap >> 8)) & (col_mask >> (tap & 255)) & 1u) != 0; };
             const int kb_all = loaded_part * kblocks + c.kb;       // k-block within the whole of K
             const int k0 = kb_all * BK;
             if(MODE == A_STRIDED) {
@@ -625,7 +632,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 const int cb = kb_all / p.num_taps, t = kb_all - cb * p.num_taps;
                 const int d = __ldg(p.tap_dydx + t);
                 const float *src = p.a + r.base + (long long)(cb * BK) * p.a_k_stride + (d >> 16) * p.in_w + (d & 0xffff);
-                if((tap_mask >> t) & 1ull) {
+                if(r.valid && unsigned(r.iy0 + (d >> 16)) < unsigned(p.in_h) && unsigned(r.ix0 + (d & 0xffff)) < unsigned(p.in_w)) {
                     #pragma unroll
                     for(int i = 0; i < BK; i++) buf[i] = __ldg(src + (long long)i * p.a_k_stride);
                 }
@@ -636,12 +643,30 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             }
             else {
                 const float *src = p.a + r.base;
-                const int2 *tab = reinterpret_cast<const int2 *>(p.ktab + k0);
-                #pragma unroll
-                for(int i = 0; i < BK; i++) {
-                    const int2 t = __ldg(tab + i);          // offset, tap number (63 = padding beyond K: never valid)
-                    const bool ok = (tap_mask >> t.y) & 1ull;
-                    buf[i] = ok ? __ldg(src + t.x) : 0.0f;
+                if(ktab_smem_entries > 0) {
+                    // table entries from shared memory, two per load, eight elements at a time: the table reads of a
+                    // batch are in flight together instead of each element waiting for its own entry
+                    const int4 *tab = ktab_s + k0 / 2;
+                    #pragma unroll
+                    for(int i0 = 0; i0 < BK; i0 += 8) {
+                        int4 e[4];
+                        #pragma unroll
+                        for(int j = 0; j < 4; j++) e[j] = tab[i0 / 2 + j];
+                        #pragma unroll
+                        for(int j = 0; j < 4; j++) {
+                            buf[i0 + 2 * j] = tap_inside(e[j].y) ? __ldg(src + e[j].x) : 0.0f;
+                            buf[i0 + 2 * j + 1] = tap_inside(e[j].w) ? __ldg(src + e[j].z) : 0.0f;
+                        }
+                    }
+                }
+                else {
+                    const int2 *tab = reinterpret_cast<const int2 *>(p.ktab + k0);
+                    #pragma unroll
+                    for(int i = 0; i < BK; i++) {
+                        const int2 t = __ldg(tab + i);          // offset, tap number (63 = padding beyond K: never valid)
+                        const bool ok = tap_inside(t.y);
+                        buf[i] = ok ? __ldg(src + t.x) : 0.0f;
+                    }
                 }
             }
         };
@@ -826,10 +851,13 @@ int choose_splits(long long rows, const TcPacked &L)
 template<int BN, int MODE>
 dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream, int splits, long long split_stride)
 {
-    const int smem = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int(sizeof(tc::Shared));
+    // the gather table rides along in shared memory when it is at most 8 KB (1024 entries: K up to 1024)
+    const int ktab_entries = MODE == A_GATHER && L.k_pad <= 1024 && p.ktab != nullptr ? L.k_pad : 0;
+    const int smem = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int((sizeof(tc::Shared) + 15) & ~size_t(15)) + ktab_entries * 8;
+    const int smem_max = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int((sizeof(tc::Shared) + 15) & ~size_t(15)) + 1024 * 8;
     static bool configured = false;   // per instantiation; the attribute is per function, set once per process
     if(!configured) {
-        DLP_CUDA_OK(cudaFuncSetAttribute(tc::contraction_tf32x3_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        DLP_CUDA_OK(cudaFuncSetAttribute(tc::contraction_tf32x3_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
         configured = true;
     }
     const long long m_tiles = ceil_div<long long>(p.rows, tc::BM);
@@ -851,7 +879,7 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packe
     int *status = device_status_word();
     if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
     tc::contraction_tf32x3_kernel<BN, MODE><<<grid, tc::NUM_THREADS, smem, stream>>>(packed, p, L.k_pad / tc::BK / splits, n_tiles, num_tiles,
-                                                                                     splits, split_stride, status, diag, trace);
+                                                                                     splits, split_stride, ktab_entries, status, diag, trace);
     DLP_LAUNCH_OK("contraction_tf32x3_kernel");
 #ifdef DLP_TC_DIAGNOSTICS
     if(trace) {
