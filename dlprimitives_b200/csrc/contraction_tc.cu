@@ -339,6 +339,11 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
     int4 *ktab_s = reinterpret_cast<int4 *>(smem + STAGES * B_STAGE_BYTES + BN * BM * 4 + ((sizeof(Shared) + 15) & ~size_t(15)));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Short K (one or two k-blocks per tile): the tile's time is its epilogue, not its MMAs.  Then one loader
+    // group feeds all k-blocks and the warps of the other group become a second set of epilogue warps,
+    // each set taking every other group of 32 columns.
+    const bool short_k = kblocks <= 2 && BN >= 128;
+    const int acc_sets = short_k ? 2 : 1;
 
     if(threadIdx.x == 0) {
         for(int s = 0; s < STAGES; s++) {
@@ -348,7 +353,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         for(int s = 0; s < STAGES / 2; s++) mbar_init(&sh->empty[s], 1);
         for(int a = 0; a < 2; a++) {
             mbar_init(&sh->acc_full[a], 1);
-            mbar_init(&sh->acc_empty[a], NUM_ACC_WARPS);
+            mbar_init(&sh->acc_empty[a], NUM_ACC_WARPS * acc_sets);
         }
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
@@ -470,9 +475,10 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
     else if(warp < WARP_ACC0) {
         // warps 2 and 3: no role
     }
-    else if(warp < WARP_LOAD0) {
+    else if(warp < WARP_LOAD0 || (short_k && warp >= WARP_LOAD0 + 4)) {
         // ------------------------------------------------------------------ accumulate + epilogue
         const int quad = warp & 3;                          // tensor-memory lanes this warp may touch
+        const int acc_set = warp < WARP_LOAD0 ? 0 : 1;      // which of the acc_sets sets of epilogue warps this one is in
         const int row_in_tile = quad * 32 + lane;
         float *my_sums = sums + row_in_tile;                // element (col) at my_sums[col * BM]: conflict-free
         const int chunks_per_tile = (kblocks + CHUNK_KB - 1) / CHUNK_KB;
@@ -505,11 +511,11 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + buf * BN;
                 #pragma unroll 1
-                for(int g = 0; g < GROUPS; g++) {
+                for(int g = acc_set; g < GROUPS; g += acc_sets) {
                     uint32_t v[G];
                     float res[G];
                     __syncwarp();
-                    if(quad == 0 && lane == 0) TC_TRACE(9, chunk * GROUPS + g);
+                    if(warp == WARP_ACC0 && lane == 0) TC_TRACE(9, chunk * GROUPS + g);
                     tmem_ld(taddr + g * G, v);
                     if(last && with_res) {
                         // the residual operand of these columns travels while the tensor-memory load does
@@ -518,8 +524,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                         for(int j = 0; j < G; j++) { res[j] = __ldg(rp); rp += col_stride; }
                     }
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if(quad == 0 && lane == 0) TC_TRACE(10, chunk * GROUPS + g);
-                    if(g == GROUPS - 1) {
+                    if(warp == WARP_ACC0 && lane == 0) TC_TRACE(10, chunk * GROUPS + g);
+                    if(g + acc_sets >= GROUPS) {
                         // the partial accumulator is fully read: hand it back to the MMA issuer
                         tc_fence_before();
                         __syncwarp();
@@ -560,7 +566,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                                 if(col0 + j < p.cols) p.y[part * split_stride + out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, sg[j * BM]);
                         }
                     }
-                    if(quad == 0 && lane == 0) TC_TRACE(11, chunk * GROUPS + g);
+                    if(warp == WARP_ACC0 && lane == 0) TC_TRACE(11, chunk * GROUPS + g);
                 }
             }
         }
@@ -568,7 +574,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
     else {
         // ------------------------------------------------------------------ A loaders
         const int quad = warp & 3;                       // tensor-memory lanes this warp may touch
-        const int group = (warp - WARP_LOAD0) >> 2;      // this warp handles k-blocks with (it & 1) == group
+        const int groups = short_k ? 1 : 2;              // loader groups taking the k-blocks in turn
+        const int group = (warp - WARP_LOAD0) >> 2;      // this warp handles k-blocks with (it % groups) == group
         const int row_in_tile = quad * 32 + lane;
         long long loaded_tile = -1, loaded_row_tile = 0;      // Cursor::tile counts work items
         int loaded_part = 0;
@@ -722,7 +729,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             for(int i = 0; i < BK; i++) cur_buf[i] = nxt_buf[i];
             cur = nxt;
             have_cur = true;
-            advance(nxt, 2);
+            advance(nxt, groups);
         }
     }
 
