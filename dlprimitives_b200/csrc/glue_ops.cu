@@ -41,10 +41,13 @@ __global__ void pooling2d_kernel(const float *__restrict__ x, float *__restrict_
 // Pooling through shared memory: a CTA takes a band of output rows of one plane, reads the input rows
 // the band needs once with coalesced (16-byte when aligned) loads, then every thread computes outputs
 // from shared memory.  The arithmetic is the same as pooling2d_kernel's, in the same order.
+// K, S: kernel size and stride when square and known at compile time (the window loops unroll), 0 = run-time values.
+template<int K, int S>
 __global__ void pooling2d_band_kernel(const float *__restrict__ x, float *__restrict__ y, long long bands_total, int bands_per_plane,
-                                      int band_rows, int in_h, int in_w, int out_h, int out_w, int kh, int kw, int sh, int sw, int ph,
+                                      int band_rows, int in_h, int in_w, int out_h, int out_w, int kh_, int kw_, int sh_, int sw_, int ph,
                                       int pw, int mode_avg, int include_pad, int vec_ok)
 {
+    const int kh = K ? K : kh_, kw = K ? K : kw_, sh = S ? S : sh_, sw = S ? S : sw_;
     extern __shared__ float tile[];
     for(long long band = blockIdx.x; band < bands_total; band += gridDim.x) {
         const long long plane = band / bands_per_plane;
@@ -72,11 +75,26 @@ __global__ void pooling2d_band_kernel(const float *__restrict__ x, float *__rest
             row0 = max(row0, 0); col0 = max(col0, 0);
             row1 = min(row1, in_h); col1 = min(col1, in_w);
             float val = mode_avg ? 0.0f : -FLT_MAX;
-            for(int r = row0; r < row1; r++)
-                for(int c = col0; c < col1; c++) {
-                    const float v = tile[(r - irow0) * in_w + c];
-                    val = mode_avg ? val + v : fmaxf(val, v);
-                }
+            if(K) {
+                // same elements in the same order as the run-time loops, with the window unrolled
+                const int wr0 = (orow0 + orel) * sh - ph, wc0 = oc * sw - pw;
+                #pragma unroll
+                for(int i2 = 0; i2 < (K ? K : 1); i2++)
+                    #pragma unroll
+                    for(int j2 = 0; j2 < (K ? K : 1); j2++) {
+                        const int r = wr0 + i2, c = wc0 + j2;
+                        if(r >= row0 && r < row1 && c >= col0 && c < col1) {
+                            const float v = tile[(r - irow0) * in_w + c];
+                            val = mode_avg ? val + v : fmaxf(val, v);
+                        }
+                    }
+            }
+            else
+                for(int r = row0; r < row1; r++)
+                    for(int c = col0; c < col1; c++) {
+                        const float v = tile[(r - irow0) * in_w + c];
+                        val = mode_avg ? val + v : fmaxf(val, v);
+                    }
             if(mode_avg) {
                 const int dr = row1 - row0, dc = col1 - col0;
                 if(dr == kh && dc == kw) val = val * (1.0f / (kh * kw));
@@ -241,9 +259,14 @@ dlp_status dlp_pooling2d_fwd(const float *x, float *y, int planes, int in_h, int
             const size_t smem = (size_t(band_rows - 1) * stride[0] + kernel[0]) * row_bytes;
             const int vec_ok = in_w % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
             const int grid = int(std::min<long long>(bands_total, (long long)sm_count() * 16));
-            pooling2d_band_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(x, y, bands_total, bands_per_plane, band_rows, in_h, in_w, oh, ow,
-                                                                             kernel[0], kernel[1], stride[0], stride[1], pad[0], pad[1], mode,
-                                                                             count_include_pad, vec_ok);
+            const bool square = kernel[0] == kernel[1] && stride[0] == stride[1];
+#define DLP_POOL_BAND(K, S) pooling2d_band_kernel<K, S><<<grid, 256, smem, (cudaStream_t)stream>>>(x, y, bands_total, bands_per_plane, band_rows, \
+            in_h, in_w, oh, ow, kernel[0], kernel[1], stride[0], stride[1], pad[0], pad[1], mode, count_include_pad, vec_ok)
+            if(square && kernel[0] == 3 && stride[0] == 2) DLP_POOL_BAND(3, 2);
+            else if(square && kernel[0] == 2 && stride[0] == 2) DLP_POOL_BAND(2, 2);
+            else if(square && kernel[0] == 3 && stride[0] == 1) DLP_POOL_BAND(3, 1);
+            else DLP_POOL_BAND(0, 0);
+#undef DLP_POOL_BAND
             DLP_LAUNCH_OK("pooling2d_band_kernel");
             return DLP_OK;
         }
