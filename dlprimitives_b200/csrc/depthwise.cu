@@ -30,7 +30,8 @@ struct DwParams {
     float factor;
 };
 
-template<int KS>
+// KS, ST: kernel size and stride known at compile time (0, 0: run-time values, any size up to 7).
+template<int KS, int ST>
 __global__ void __launch_bounds__(THREADS) depthwise_kernel(DwParams p)
 {
     __shared__ __align__(16) float tile[SMEM_FLOATS];
@@ -66,6 +67,59 @@ __global__ void __launch_bounds__(THREADS) depthwise_kernel(DwParams p)
     __syncthreads();
 
     const int out_rows = oy1 - oy0;
+    if(KS > 0) {
+        // A thread takes one output column of up to R consecutive output rows: the index arithmetic and the
+        // filter (kept in registers) are paid once per R outputs, each input row is read once and feeds
+        // every output row it belongs to, and the lanes of a warp read consecutive shared-memory words.
+        // Per output the products are added in the same order (ky, then kx) as in the general loop below.
+        constexpr int R = 4;
+        constexpr int IN_ROWS = (R - 1) * (ST > 0 ? ST : 1) + (KS > 0 ? KS : 1);
+        const int segs = (out_rows + R - 1) / R;
+        const int items = np * segs * p.OW;
+        for(int it = threadIdx.x; it < items; it += THREADS) {
+            const int ox = it % p.OW, t2 = it / p.OW;
+            const int seg = t2 % segs, pl = t2 / segs;
+            const long long plane = plane0 + pl;
+            const int c = int(plane % p.channels);
+            float wreg[(KS > 0 ? KS : 1) * (KS > 0 ? KS : 1)];
+            #pragma unroll
+            for(int i = 0; i < KS * KS; i++) wreg[i] = __ldg(p.w + (long long)c * (KS * KS) + i);
+            const int oyb = oy0 + seg * R, nr = min(R, oy1 - oyb);
+            const int iyb = oyb * ST - p.pad, ix0 = ox * ST - p.pad;
+            const float *src = tile + shift + (long long)pl * plane_elems - (long long)iy_lo * p.W;
+            float acc[R];
+            #pragma unroll
+            for(int j = 0; j < R; j++) acc[j] = 0.0f;
+            #pragma unroll
+            for(int rr = 0; rr < IN_ROWS; rr++) {
+                const int iy = iyb + rr;
+                if(rr >= (nr - 1) * ST + KS || unsigned(iy) >= unsigned(p.H)) continue;
+                float v[KS > 0 ? KS : 1];
+                #pragma unroll
+                for(int kx = 0; kx < KS; kx++) v[kx] = unsigned(ix0 + kx) < unsigned(p.W) ? src[iy * p.W + ix0 + kx] : 0.0f;
+                #pragma unroll
+                for(int j = 0; j < R; j++) {
+                    const int ky = rr - j * ST;        // compile-time after unrolling
+                    if(ky < 0 || ky >= KS) continue;
+                    #pragma unroll
+                    for(int kx = 0; kx < KS; kx++)
+                        if(unsigned(ix0 + kx) < unsigned(p.W)) acc[j] = fmaf(v[kx], wreg[ky * KS + kx], acc[j]);
+                }
+            }
+            const float b = p.bias ? __ldg(p.bias + c) : 0.0f;
+            #pragma unroll
+            for(int j = 0; j < R; j++) {
+                if(j >= nr) break;
+                float a = acc[j];
+                if(p.bias) a += b;
+                a = apply_act(a, p.act);
+                const long long yi = plane * ((long long)p.OH * p.OW) + (long long)(oyb + j) * p.OW + ox;
+                if(p.factor != 0.0f) a += p.factor * p.y[yi];
+                p.y[yi] = a;
+            }
+        }
+        return;
+    }
     const int outs_per_plane = out_rows * p.OW;
     const int total_out = np * outs_per_plane;
     for(int o = threadIdx.x; o < total_out; o += THREADS) {
@@ -80,14 +134,10 @@ __global__ void __launch_bounds__(THREADS) depthwise_kernel(DwParams p)
         const float *src = tile + shift + (long long)pl * plane_elems - (long long)iy_lo * p.W;
         const int iy0 = oy * p.stride - p.pad, ix0 = ox * p.stride - p.pad;
         float acc = 0.0f;
-        #pragma unroll
-        for(int ky = 0; ky < (KS > 0 ? KS : 7); ky++) {
-            if(KS == 0 && ky >= ks) break;
+        for(int ky = 0; ky < ks; ky++) {
             const int iy = iy0 + ky;
             if(unsigned(iy) >= unsigned(p.H)) continue;
-            #pragma unroll
-            for(int kx = 0; kx < (KS > 0 ? KS : 7); kx++) {
-                if(KS == 0 && kx >= ks) break;
+            for(int kx = 0; kx < ks; kx++) {
                 const int ix = ix0 + kx;
                 if(unsigned(ix) >= unsigned(p.W)) continue;
                 acc = fmaf(src[iy * p.W + ix], __ldg(wk + ky * ks + kx), acc);
@@ -144,10 +194,12 @@ dlp_status launch_depthwise(const float *x, const float *w, const float *bias, f
     }
     const long long blocks = ceil_div<long long>(p.planes, p.planes_per_cta) * p.bands;
     if(blocks > 0x7fffffffLL) return fail(DLP_INVALID_ARGUMENT, "depthwise problem too large for one launch");
-    switch(ks) {
-    case 3: depthwise_kernel<3><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
-    case 5: depthwise_kernel<5><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
-    default: depthwise_kernel<0><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
+    switch(ks * 10 + stride) {
+    case 31: depthwise_kernel<3, 1><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
+    case 32: depthwise_kernel<3, 2><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
+    case 51: depthwise_kernel<5, 1><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
+    case 52: depthwise_kernel<5, 2><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
+    default: depthwise_kernel<0, 0><<<(unsigned)blocks, THREADS, 0, stream>>>(p); break;
     }
     DLP_LAUNCH_OK("depthwise_kernel");
     return DLP_OK;
