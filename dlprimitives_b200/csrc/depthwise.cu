@@ -54,68 +54,91 @@ __global__ void __launch_bounds__(THREADS) depthwise_kernel(DwParams p)
     const int shift = int(g_begin - a_begin);
     const int count = int(g_end - a_begin);
 
-    for(int i = threadIdx.x * 4; i < count; i += THREADS * 4) {
-        const long long gi = a_begin + i;
-        if(gi + 4 <= total_in) {
-            const float4 v = __ldg(reinterpret_cast<const float4 *>(p.x + gi));
-            *reinterpret_cast<float4 *>(tile + i) = v;
+    // copy in: four 16-byte loads in flight per thread before their stores, then the ragged rest
+    {
+        constexpr int U = 4;
+        const int safe = int(min((long long)count, total_in - a_begin)) & ~3;      // whole float4s inside the tensor
+        int i = threadIdx.x * 4;
+        for(; i + (U - 1) * THREADS * 4 < safe; i += U * THREADS * 4) {
+            float4 v[U];
+            #pragma unroll
+            for(int u = 0; u < U; u++) v[u] = __ldg(reinterpret_cast<const float4 *>(p.x + a_begin + i + u * THREADS * 4));
+            #pragma unroll
+            for(int u = 0; u < U; u++) *reinterpret_cast<float4 *>(tile + i + u * THREADS * 4) = v[u];
         }
-        else {
-            for(int j = 0; j < 4 && gi + j < total_in; j++) tile[i + j] = __ldg(p.x + gi + j);
+        for(; i < count; i += THREADS * 4) {
+            const long long gi = a_begin + i;
+            if(i + 4 <= safe) *reinterpret_cast<float4 *>(tile + i) = __ldg(reinterpret_cast<const float4 *>(p.x + gi));
+            else
+                for(int j = 0; j < 4 && gi + j < total_in; j++) tile[i + j] = __ldg(p.x + gi + j);
         }
     }
     __syncthreads();
 
     const int out_rows = oy1 - oy0;
     if(KS > 0) {
-        // A thread takes one output column of up to R consecutive output rows: the index arithmetic and the
-        // filter (kept in registers) are paid once per R outputs, each input row is read once and feeds
-        // every output row it belongs to, and the lanes of a warp read consecutive shared-memory words.
-        // Per output the products are added in the same order (ky, then kx) as in the general loop below.
-        constexpr int R = 4;
+        // A thread takes a patch of CW adjacent output columns by up to R consecutive output rows: the index
+        // arithmetic and the filter (kept in registers) are paid once per patch, each input value is read
+        // from shared memory once and feeds every output of the patch it belongs to.  Per output the
+        // products are added in the same order (ky, then kx) as in the general loop below.
+        constexpr int R = 4, CW = 2;
         constexpr int IN_ROWS = (R - 1) * (ST > 0 ? ST : 1) + (KS > 0 ? KS : 1);
-        const int segs = (out_rows + R - 1) / R;
-        const int items = np * segs * p.OW;
+        constexpr int IN_COLS = (CW - 1) * (ST > 0 ? ST : 1) + (KS > 0 ? KS : 1);
+        const int segs = (out_rows + R - 1) / R, colp = (p.OW + CW - 1) / CW;
+        const int items = np * segs * colp;
         for(int it = threadIdx.x; it < items; it += THREADS) {
-            const int ox = it % p.OW, t2 = it / p.OW;
+            const int oxp = it % colp, t2 = it / colp;
             const int seg = t2 % segs, pl = t2 / segs;
             const long long plane = plane0 + pl;
             const int c = int(plane % p.channels);
             float wreg[(KS > 0 ? KS : 1) * (KS > 0 ? KS : 1)];
             #pragma unroll
             for(int i = 0; i < KS * KS; i++) wreg[i] = __ldg(p.w + (long long)c * (KS * KS) + i);
+            const int ox0 = oxp * CW, nc = min(CW, p.OW - ox0);
             const int oyb = oy0 + seg * R, nr = min(R, oy1 - oyb);
-            const int iyb = oyb * ST - p.pad, ix0 = ox * ST - p.pad;
+            const int iyb = oyb * ST - p.pad, ix0 = ox0 * ST - p.pad;
             const float *src = tile + shift + (long long)pl * plane_elems - (long long)iy_lo * p.W;
-            float acc[R];
+            unsigned col_ok = 0;      // bit i: input column ix0 + i is inside the image
             #pragma unroll
-            for(int j = 0; j < R; j++) acc[j] = 0.0f;
+            for(int i = 0; i < IN_COLS; i++)
+                if(unsigned(ix0 + i) < unsigned(p.W)) col_ok |= 1u << i;
+            float acc[R][CW];
+            #pragma unroll
+            for(int j = 0; j < R; j++)
+                #pragma unroll
+                for(int cc = 0; cc < CW; cc++) acc[j][cc] = 0.0f;
             #pragma unroll
             for(int rr = 0; rr < IN_ROWS; rr++) {
                 const int iy = iyb + rr;
                 if(rr >= (nr - 1) * ST + KS || unsigned(iy) >= unsigned(p.H)) continue;
-                float v[KS > 0 ? KS : 1];
+                float v[IN_COLS];
                 #pragma unroll
-                for(int kx = 0; kx < KS; kx++) v[kx] = unsigned(ix0 + kx) < unsigned(p.W) ? src[iy * p.W + ix0 + kx] : 0.0f;
+                for(int i = 0; i < IN_COLS; i++) v[i] = (col_ok >> i) & 1u ? src[iy * p.W + ix0 + i] : 0.0f;
                 #pragma unroll
                 for(int j = 0; j < R; j++) {
                     const int ky = rr - j * ST;        // compile-time after unrolling
                     if(ky < 0 || ky >= KS) continue;
                     #pragma unroll
-                    for(int kx = 0; kx < KS; kx++)
-                        if(unsigned(ix0 + kx) < unsigned(p.W)) acc[j] = fmaf(v[kx], wreg[ky * KS + kx], acc[j]);
+                    for(int cc = 0; cc < CW; cc++)
+                        #pragma unroll
+                        for(int kx = 0; kx < KS; kx++)
+                            if((col_ok >> (cc * ST + kx)) & 1u) acc[j][cc] = fmaf(v[cc * ST + kx], wreg[ky * KS + kx], acc[j][cc]);
                 }
             }
             const float b = p.bias ? __ldg(p.bias + c) : 0.0f;
             #pragma unroll
             for(int j = 0; j < R; j++) {
                 if(j >= nr) break;
-                float a = acc[j];
-                if(p.bias) a += b;
-                a = apply_act(a, p.act);
-                const long long yi = plane * ((long long)p.OH * p.OW) + (long long)(oyb + j) * p.OW + ox;
-                if(p.factor != 0.0f) a += p.factor * p.y[yi];
-                p.y[yi] = a;
+                #pragma unroll
+                for(int cc = 0; cc < CW; cc++) {
+                    if(cc >= nc) break;
+                    float a = acc[j][cc];
+                    if(p.bias) a += b;
+                    a = apply_act(a, p.act);
+                    const long long yi = plane * ((long long)p.OH * p.OW) + (long long)(oyb + j) * p.OW + ox0 + cc;
+                    if(p.factor != 0.0f) a += p.factor * p.y[yi];
+                    p.y[yi] = a;
+                }
             }
         }
         return;
@@ -180,8 +203,8 @@ dlp_status launch_depthwise(const float *x, const float *w, const float *bias, f
         p.bands = 1;
         p.rows_per_band = p.OH;
         int ppc = int(budget / plane_elems);
-        // keep at least ~4 CTAs per SM worth of blocks when the problem allows
-        const int want_blocks = 4 * sm_count();
+        // several waves of CTAs per SM when the problem allows, so that copy-in and compute phases of different CTAs overlap
+        const int want_blocks = 16 * sm_count();
         ppc = std::max(1, std::min(ppc, int(ceil_div<long long>(p.planes, want_blocks))));
         p.planes_per_cta = ppc;
     }
