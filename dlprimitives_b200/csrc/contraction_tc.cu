@@ -41,8 +41,8 @@ constexpr int A_COL_BASE = 256;      // tensor-memory columns [0,256): two parti
 constexpr int TMEM_COLS = 512;
 constexpr int CHUNK_KB = 8;          // k-blocks summed inside the tensor core before the sum moves to fp32 adds
 // Warp roles.  Tensor-memory lanes are tied to (warp index mod 4), so the accumulate and the loader
-// warps start at multiples of four (warps 2 and 3 have no role).
-constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_ACC0 = 4, WARP_LOAD0 = 8;
+// warps start at multiples of four (warp 2 prefetches the residual operand into L2, warp 3 has no role).
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_PREFETCH = 2, WARP_ACC0 = 4, WARP_LOAD0 = 8;
 constexpr int NUM_ACC_WARPS = 4, NUM_LOADER_WARPS = 8;
 constexpr int NUM_WARPS = WARP_LOAD0 + NUM_LOADER_WARPS;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
@@ -68,6 +68,7 @@ struct Shared {
     int abort_flag;
     uint32_t tma_issued;     // k-blocks whose bulk copies were issued
     uint32_t mma_consumed;   // the first k-block the MMA issuer has not taken up
+    uint32_t epilogue_started;   // work items of this CTA whose partial sums the accumulate warps have begun to read
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -359,6 +360,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         sh->abort_flag = 0;
         sh->tma_issued = 0;
         sh->mma_consumed = 0;
+        sh->epilogue_started = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if(warp == WARP_MMA) {
@@ -472,8 +474,44 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         }
         if(lane == 0) *(volatile uint32_t *)&sh->mma_consumed = it;
     }
+    else if(warp == WARP_PREFETCH) {
+        // ------------------------------------------------------------------ residual prefetcher
+        // The epilogue of a tile reads its residual operand with 128 strided loads per thread; from HBM
+        // their latency is most of the epilogue's time.  This warp asks for the residual tile of the
+        // CTA's next work item to be brought into L2 while the current one is still being computed: one
+        // tile ahead.  It only ever gives hints: if its pacing wait runs out it simply stops.
+        // Worth it (measured) when a tile has 3 to 8 k-blocks: with fewer the tiles are too short to stay a tile
+        // ahead, with more the MMAs hide the epilogue anyway.
+        if(p.residual != nullptr && !short_k && kblocks <= CHUNK_KB) {
+            // item index i of this CTA is prefetched once the accumulate warps have started on item i - 1
+            // (a counter they publish); when this warp has fallen behind it skips to where they are
+            uint32_t i = 0;
+            for(long long item = blockIdx.x; item < num_tiles; item += gridDim.x, i++) {
+                uint32_t started = *(volatile uint32_t *)&sh->epilogue_started;
+                for(int tries = 0; started < i && tries < (1 << 14); tries++) {
+                    __nanosleep(64);
+                    started = *(volatile uint32_t *)&sh->epilogue_started;
+                }
+                if(started < i) break;              // no progress for a long time: stop giving hints
+                if(started > i + 1) continue;       // behind: this tile's residual is being read already
+                long long tile;
+                int part;
+                decode_item(item, splits, tile, part);
+                const int n0 = int(tile % n_tiles) * BN;
+                const long long row0 = (tile / n_tiles) * BM;
+                // every 16th row of the tile (64 bytes apart in a channel plane), and its last row: touches every line
+                #pragma unroll 1
+                for(int j = 0; j <= BM / 16; j++) {
+                    const RowInfo r = make_row(p, row0 + min(16 * j, BM - 1));
+                    if(!r.valid) break;
+                    for(int c = lane; c < BN && n0 + c < p.cols; c += 32)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + out_index(p, r, n0 + c)));
+                }
+            }
+        }
+    }
     else if(warp < WARP_ACC0) {
-        // warps 2 and 3: no role
+        // warp 3: no role
     }
     else if(warp < WARP_LOAD0 || (short_k && warp >= WARP_LOAD0 + 4)) {
         // ------------------------------------------------------------------ accumulate + epilogue
@@ -482,7 +520,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         const int row_in_tile = quad * 32 + lane;
         float *my_sums = sums + row_in_tile;                // element (col) at my_sums[col * BM]: conflict-free
         const int chunks_per_tile = (kblocks + CHUNK_KB - 1) / CHUNK_KB;
-        uint32_t chunk = 0;
+        uint32_t chunk = 0, items_begun = 0;
         // identity / relu / relu6 are a clamp; with no per-row bias and no beta the whole epilogue is
         // add, clamp, (residual, clamp,) store.  Anything else takes the general path.
         const float2 clamp = act_clamp(p.act), post_clamp = act_clamp(p.post_act);
@@ -508,6 +546,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 const uint32_t buf = chunk & 1;
                 const bool first = c == 0, last = c == chunks_per_tile - 1;
                 if(!warp_wait(&sh->acc_full[buf], (chunk >> 1) & 1, sh, status, ST_EPI_ACC, lane)) { live = false; break; }
+                if(c == 0 && warp == WARP_ACC0 && lane == 0) *(volatile uint32_t *)&sh->epilogue_started = ++items_begun;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + buf * BN;
                 #pragma unroll 1
