@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Headline benchmark: ResNet-50 fp32 inference images/s on 1/2/4/8 B200 (BASELINE.json config 5).
+"""Headline benchmark: ResNet-50 fp32 inference, global batch 256, images/s on 1/2/4/8 B200.
 
 A step is one forward pass of the whole network over a global batch of 256 synthetic images, split by
 batch over the ranks (replicated weights, no communication during the pass, outputs gathered to rank 0
