@@ -307,3 +307,34 @@ def test_split_k_small_batch_matches_checker_and_is_deterministic():
         plan.enqueue(xd, wd, bd, y, ws)
         assert rel_err(y.cpu().numpy(), ob.conv2d(x, w, b, stride=1, pad=pad)) <= REL_TOL
     assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("cin,cout,hw,batch", [(40, 200, 13, 3), (64, 256, 28, 5), (96, 384, 13, 7), (128, 512, 14, 9), (256, 130, 9, 4)])
+def test_one_by_one_expansions_with_fused_residual_ragged(cin, cout, hw, batch):
+    """1x1 convolutions with the fused residual at sizes that leave partial row and column tiles and planes
+    that are not a multiple of anything: covers the short-K mode (one or two k-blocks per tile, second set of
+    epilogue warps) and the residual prefetcher (3 to 8 k-blocks)."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    ob.set_threads(16)
+    rng = np.random.default_rng(cin * 7 + cout)
+    x = rng.standard_normal((batch, cin, hw, hw), dtype=np.float32)
+    w = kaiming(rng, (cout, cin, 1, 1))
+    b = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+    res = rng.standard_normal((batch, cout, hw, hw), dtype=np.float32)
+    plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=1, batch=batch, height=hw, width=hw, bias=True, activation="identity")
+    assert plan.kernel().startswith("igemm_tf32x3_bn128")
+    xd, wd, bd, rd = to_dev(x), to_dev(w), to_dev(b), to_dev(res)
+    packed = plan.prepack(wd)
+    want = np.maximum(ob.conv2d(x, w, b) + 0.5 * res, 0.0)
+    for _ in range(2):
+        y = torch.full(plan.output_shape(batch), float("nan"), device=DEV)
+        plan.enqueue_packed(xd, packed, bd, y, residual=rd, residual_scale=0.5, post_activation="relu")
+        got = y.cpu().numpy()
+        assert not np.isnan(got).any()
+        assert rel_err(got, want) <= REL_TOL
+    # residual aliasing the output, as the reference's in-place Elementwise allows
+    y = rd.clone()
+    plan.enqueue_packed(xd, packed, bd, y, residual=y, residual_scale=0.5, post_activation="relu")
+    assert rel_err(y.cpu().numpy(), want) <= REL_TOL
+    assert capi.device_status() == 0
