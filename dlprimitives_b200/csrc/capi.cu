@@ -182,17 +182,19 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
         // an incompatible "winograd" or "depthwise_separable" request gets the GEMM algorithm, as in the
         // reference (src/core/conv.cpp:719-727)
         plan->algo = "gemm";
-        // the tensor-core loader keeps one validity bit per kernel tap in a 64-bit word
-        // (and one validity bit per kernel row and column in 32-bit words, bit 31 standing for "never")
-        const bool tc_ok = d.groups == 1 && d.math_mode != DLP_MATH_FP32_FFMA && d.kernel[0] * d.kernel[1] <= MAX_TAPS &&
-                           d.kernel[0] <= 30 && d.kernel[1] <= 30;
+        // the tensor-core loaders keep one validity bit per kernel row and per kernel column in 32-bit words
+        // (bit 31 stands for "never")
+        // Grouped convolutions run group by group (a launch each) when a group is wide enough to be worth a tile
+        // and there are few of them; the rest stay on the grouped FFMA kernel.
+        const bool groups_ok = d.groups == 1 || (d.groups <= 16 && d.channels_in / d.groups >= 8 && d.channels_out / d.groups >= 16);
+        const bool tc_ok = groups_ok && d.math_mode != DLP_MATH_FP32_FFMA && d.kernel[0] <= MAX_KERNEL_SIDE && d.kernel[1] <= MAX_KERNEL_SIDE;
         if(d.math_mode == DLP_MATH_TF32X3 && !tc_ok)
-            return fail(DLP_NOT_IMPLEMENTED, "the tensor-core kernel handles groups == 1 and kernels of at most 63 taps");
+            return fail(DLP_NOT_IMPLEMENTED, "the tensor-core kernel handles at most 16 groups of at least 8 x 16 channels and kernels of at most 30 x 30");
         plan->kind = tc_ok ? CK_TC : CK_FFMA;
     }
     plan->strided_a = d.kernel[0] == 1 && d.kernel[1] == 1 && d.stride[0] == 1 && d.stride[1] == 1 && d.pad[0] == 0 && d.pad[1] == 0;
 
-    plan->tapblock = plan->kind == CK_TC && !plan->strided_a && d.channels_in % 32 == 0;
+    plan->tapblock = plan->kind == CK_TC && !plan->strided_a && (d.channels_in / d.groups) % 32 == 0;
     if(plan->kind != CK_DEPTHWISE && plan->kind != CK_WINOGRAD) {
         plan->packed = tc_packed_layout(d.channels_out / d.groups, plan->k);
         if(plan->kind == CK_TC)
@@ -244,7 +246,7 @@ size_t dlp_conv2d_fwd_packed_bytes(const dlp_conv2d_plan *plan)
 {
     if(!plan) return 0;
     if(plan->kind == CK_WINOGRAD) return winograd_packed_bytes(plan->d.channels_in, plan->d.channels_out);
-    return plan->kind == CK_TC ? plan->packed.bytes() : 0;
+    return plan->kind == CK_TC ? plan->packed.bytes() * size_t(plan->d.groups) : 0;     // one packed operand per group
 }
 size_t dlp_conv2d_fwd_workspace(const dlp_conv2d_plan *plan)
 {
@@ -263,8 +265,14 @@ dlp_status dlp_conv2d_fwd_prepack(const dlp_conv2d_plan *plan, const float *w, v
     }
     if(plan->kind != CK_TC) return DLP_OK;
     DLP_REQUIRE(packed != nullptr, "null packed buffer");
-    return tc_prepack(plan->packed, w, plan->k, 1, plan->d.channels_out, plan->k, static_cast<float *>(packed),
-                      plan->tapblock ? plan->num_taps : 0, (cudaStream_t)stream);
+    const int cout_g = plan->d.channels_out / plan->d.groups;
+    for(int g = 0; g < plan->d.groups; g++) {
+        dlp_status st = tc_prepack(plan->packed, w + (long long)g * cout_g * plan->k, plan->k, 1, cout_g, plan->k,
+                                   static_cast<float *>(packed) + g * (plan->packed.bytes() / sizeof(float)),
+                                   plan->tapblock ? plan->num_taps : 0, (cudaStream_t)stream);
+        if(st != DLP_OK) return st;
+    }
+    return DLP_OK;
 }
 
 static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, const float *w_raw, const float *packed, const float *bias,
@@ -335,7 +343,19 @@ static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, cons
 
     if(plan->kind == CK_TC) {
         DLP_REQUIRE(packed != nullptr, "null packed weights");
-        return launch_contraction_tc(p, plan->packed, packed, stream, scratch, scratch_bytes);
+        // group g: input channels [g*cin_g, ...), its own packed operand, output channels [g*cout_g, ...)
+        for(int g = 0; g < d.groups; g++) {
+            Contraction q = p;
+            q.a = x + (long long)g * cin_g * d.height * d.width;
+            const long long out_off = (long long)g * cout_g * plan->out_h * plan->out_w;
+            q.y = y + out_off;
+            if(bias) q.bias = bias + g * cout_g;
+            if(residual) q.residual = residual + out_off;
+            dlp_status st = launch_contraction_tc(q, plan->packed, packed + g * (plan->packed.bytes() / sizeof(float)), stream, scratch,
+                                                  scratch_bytes);
+            if(st != DLP_OK) return st;
+        }
+        return DLP_OK;
     }
     DLP_REQUIRE(w_raw != nullptr, "null weights");
     return launch_contraction_ffma(p, d.groups, (long long)cin_g * d.height * d.width, (long long)cout_g * plan->k, cout_g, stream);

@@ -30,7 +30,7 @@ struct KTap {
                  // TAP_PADDING for the zero padding beyond K (a kernel row that never exists)
 };
 constexpr int TAP_PADDING = 31 << 8;
-constexpr int MAX_TAPS = 63;     // kernels with more taps than bits in the per-pixel validity mask use the FFMA path
+constexpr int MAX_KERNEL_SIDE = 30;   // larger kernels (more rows or columns than validity bits) use the FFMA path
 
 struct Contraction {
     // sizes

@@ -338,3 +338,31 @@ def test_one_by_one_expansions_with_fused_residual_ragged(cin, cout, hw, batch):
     plan.enqueue_packed(xd, packed, bd, y, residual=y, residual_scale=0.5, post_activation="relu")
     assert rel_err(y.cpu().numpy(), want) <= REL_TOL
     assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("cin,cout,groups,k,hw", [(96, 192, 2, 5, 27), (64, 128, 4, 3, 14), (128, 64, 2, 1, 9)])
+def test_grouped_convolution_on_the_tensor_core_path(cin, cout, groups, k, hw):
+    """Groups that are wide enough run group by group through the tensor-core kernel (one packed operand
+    and one launch per group): checked against the CPU checker, plain and with the fused residual."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    ob.set_threads(16)
+    rng = np.random.default_rng(cin + cout + groups)
+    batch, pad = 3, k // 2
+    x = rng.standard_normal((batch, cin, hw, hw), dtype=np.float32)
+    w = kaiming(rng, (cout, cin // groups, k, k))
+    b = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+    plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, pad=pad, groups=groups, batch=batch, height=hw, width=hw,
+                              bias=True, activation="relu")
+    assert plan.kernel().startswith("igemm_tf32x3")
+    xd, wd, bd = to_dev(x), to_dev(w), to_dev(b)
+    want = ob.conv2d(x, w, b, stride=1, pad=pad, groups=groups, activation="relu")
+    y = torch.full(plan.output_shape(batch), float("nan"), device=DEV)
+    ws = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=DEV)
+    plan.enqueue(xd, wd, bd, y, ws)
+    assert rel_err(y.cpu().numpy(), want) <= REL_TOL
+    res = rng.standard_normal(want.shape, dtype=np.float32)
+    y2 = torch.full(plan.output_shape(batch), float("nan"), device=DEV)
+    plan.enqueue_packed(xd, plan.prepack(wd), bd, y2, residual=to_dev(res), post_activation="relu")
+    assert rel_err(y2.cpu().numpy(), np.maximum(want + res, 0.0)) <= REL_TOL
+    assert capi.device_status() == 0
