@@ -538,12 +538,13 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             // chunk the residual operand of the same columns is fetched under that wait as well.
             constexpr int G = BN >= 32 ? 32 : 16;
             constexpr int GROUPS = BN / G;
-            // the lean epilogue serves every group of 32 columns that lies wholly inside the matrix; a ragged last
-            // group takes the general path and groups beyond the last column are skipped
-            const bool fast_row = epi_fast && r.valid && !TC_DIAG(DIAG_NO_STORES);
-            const bool with_res_row = fast_row && p.residual != nullptr;
+            const bool fast = epi_fast && r.valid && n0 + BN <= p.cols && !TC_DIAG(DIAG_NO_STORES);
+            const bool with_res = fast && p.residual != nullptr;
             float *y_row = p.y + part * split_stride + r.out + (long long)n0 * col_stride;
-            const float *res_row = with_res_row ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
+            const float *res_row = with_res ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
+            // A tile whose last columns lie beyond the matrix takes its own, rolled path: groups of columns that do
+            // not exist are skipped and the others go column by column through the lean arithmetic when it applies.
+            const bool ragged_tile = n0 + BN > p.cols;
             for(int c = 0; c < chunks_per_tile; c++, chunk++) {
                 const uint32_t buf = chunk & 1;
                 const bool first = c == 0, last = c == chunks_per_tile - 1;
@@ -551,21 +552,52 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 if(c == 0 && warp == WARP_ACC0 && lane == 0) *(volatile uint32_t *)&sh->epilogue_started = ++items_begun;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + buf * BN;
-                #pragma unroll 1
-                for(int g = acc_set; g < GROUPS; g += acc_sets) {
-                    uint32_t v[G];
-                    float res[G];
-                    const int cols_left = p.cols - (n0 + g * G);      // warp-uniform
-                    const bool fast = fast_row && cols_left >= G, with_res = with_res_row && cols_left >= G;
-                    if(cols_left <= 0) {
-                        // nothing of this group exists; only the hand-back of the accumulator may be due
+                if(ragged_tile) {
+                    const bool lean = epi_fast && r.valid && !TC_DIAG(DIAG_NO_STORES);
+                    #pragma unroll 1
+                    for(int g = acc_set; g < GROUPS; g += acc_sets) {
+                        const int col0 = n0 + g * G, cols_left = p.cols - col0;        // warp-uniform
+                        float *sg = my_sums + g * G * BM;
+                        if(cols_left > 0) {
+                            uint32_t v[G];
+                            __syncwarp();
+                            tmem_ld(taddr + g * G, v);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            // the values pass through the thread's own slots of the sums tile so that the rolled loops can index them
+                            #pragma unroll
+                            for(int j = 0; j < G; j++) sg[j * BM] = first ? __uint_as_float(v[j]) : sg[j * BM] + __uint_as_float(v[j]);
+                        }
                         if(g + acc_sets >= GROUPS) {
                             tc_fence_before();
                             __syncwarp();
                             if(lane == 0) mbar_arrive(&sh->acc_empty[buf]);
                         }
-                        continue;
+                        if(!last || cols_left <= 0) continue;
+                        const int ncols = min(cols_left, G);
+                        if(lean) {
+                            float *y0 = y_row + (long long)(g * G) * col_stride;
+                            const float *r0 = p.residual ? p.residual + r.out + (long long)col0 * col_stride : nullptr;
+                            #pragma unroll 1
+                            for(int j = 0; j < ncols; j++) {
+                                float a = sg[j * BM];
+                                if(p.bias_mode == DLP_GEMM_BIAS_N) a += __ldg(p.bias + col0 + j);
+                                a = fminf(fmaxf(a, clamp.x), clamp.y);
+                                if(r0) a = fminf(fmaxf(a + p.residual_scale * __ldg(r0 + (long long)j * col_stride), post_clamp.x), post_clamp.y);
+                                y0[(long long)j * col_stride] = a;
+                            }
+                        }
+                        else if(r.valid && !TC_DIAG(DIAG_NO_STORES)) {
+                            #pragma unroll 1
+                            for(int j = 0; j < ncols; j++)
+                                p.y[part * split_stride + out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, sg[j * BM]);
+                        }
                     }
+                    continue;
+                }
+                #pragma unroll 1
+                for(int g = acc_set; g < GROUPS; g += acc_sets) {
+                    uint32_t v[G];
+                    float res[G];
                     __syncwarp();
                     if(warp == WARP_ACC0 && lane == 0) TC_TRACE(9, chunk * GROUPS + g);
                     tmem_ld(taddr + g * G, v);
@@ -612,20 +644,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                         // in local memory on every path)
                         #pragma unroll
                         for(int j = 0; j < G; j++) sg[j * BM] = x[j];
-                        if(fast_row) {
-                            // a ragged group of a problem the lean epilogue can serve: the same arithmetic, column by column
-                            float *y0 = y_row + (long long)(g * G) * col_stride;
-                            const float *r0 = p.residual ? p.residual + r.out + (long long)col0 * col_stride : nullptr;
-                            #pragma unroll 1
-                            for(int j = 0; j < cols_left && j < G; j++) {
-                                float a = sg[j * BM];
-                                if(p.bias_mode == DLP_GEMM_BIAS_N) a += __ldg(p.bias + col0 + j);
-                                a = fminf(fmaxf(a, clamp.x), clamp.y);
-                                if(r0) a = fminf(fmaxf(a + p.residual_scale * __ldg(r0 + (long long)j * col_stride), post_clamp.x), post_clamp.y);
-                                y0[(long long)j * col_stride] = a;
-                            }
-                        }
-                        else if(r.valid && !TC_DIAG(DIAG_NO_STORES)) {
+                        if(r.valid && !TC_DIAG(DIAG_NO_STORES)) {
                             #pragma unroll 1
                             for(int j = 0; j < G; j++)
                                 if(col0 + j < p.cols) p.y[part * split_stride + out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, sg[j * BM]);
