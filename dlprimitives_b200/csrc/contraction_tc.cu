@@ -7,21 +7,26 @@
 // hi_a*hi_b, dropping only lo_a*lo_b (relative size 2^-22).
 //
 // Data flow per CTA (persistent, one CTA per SM, 128-row x BN-column output tiles, K in blocks of 32):
-//   * B (weights) is split once, when it is packed: the packed operand holds, per column tile, the hi
-//     rows followed by the lo rows.  One bulk tensor copy per k-block brings both tiles into a
-//     128B-swizzled shared-memory ring, several k-blocks ahead of use.
+//   * B (weights) is split once, when it is packed: the packed operand is the sequence of pipeline
+//     stages (column tile, k-block), each the exact shared-memory image of the k-block's hi tile
+//     followed by its lo tile (128B-swizzled).  One contiguous bulk copy per k-block brings a stage
+//     into a shared-memory ring, up to four k-blocks ahead of use.
 //   * A (activations): loader warps read the caller's NCHW tensor directly (implicit im2col, no
 //     re-layout in memory), split each value in registers and write hi/lo with tcgen05.st into a
 //     ring of tensor-memory columns.  The MMA takes A from tensor memory and B from shared memory,
 //     which keeps the shared-memory read traffic of the three products at one operand.  The tensor
 //     core reads only the TF32 part of an fp32 word, so the unsplit value serves as hi.
-//   * one thread issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8).
+//   * one elected thread of a warp-uniform loop issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), twelve
+//     per k-block, testing the next k-block's barriers while they go out.
 //   * the tensor core adds into its fp32 accumulator with truncation, which over thousands of steps
 //     shows up as a systematic shrink of the result.  So a tensor-memory accumulator only ever holds
 //     the partial sum of CHUNK_KB k-blocks (two such buffers alternate); accumulate warps add the
 //     partial sums into a shared-memory tile with ordinary round-to-nearest fp32 adds, and on the
 //     tile's last chunk apply bias / activation / residual / beta and store straight to NCHW
 //     (32 consecutive pixels per warp store) or row-major.
+//   * variations: tiles of one or two k-blocks borrow a loader group as a second set of epilogue warps;
+//     a spare warp hints the next tile's residual operand into L2; problems with too few tiles are cut
+//     along K into extra work items whose partial sums a finishing kernel adds in a fixed order.
 //
 // All mbarrier waits are bounded: a wait that gives up records a code in the device status word,
 // raises the CTA's abort flag, and every role then leaves its loop; the CTA drains its bulk copies
