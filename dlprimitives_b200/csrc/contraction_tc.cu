@@ -417,65 +417,81 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO, version 1, SWIZZLE_128B
         const uint32_t ring_base = ((smem_u32(b_ring) & 0x3FFFF) >> 4) | (1u << 16);
         const uint32_t acc_empty0 = smem_u32(&sh->acc_empty[0]), empty0 = smem_u32(&sh->empty[0]), acc_full0 = smem_u32(&sh->acc_full[0]);
-        // the barrier array this lane watches (8 bytes per entry): lane 0 the A columns, lane 1 the B tiles
-        const uint32_t watch_base = smem_u32(lane == 1 ? &sh->full_b[0] : &sh->full_a[0]);
+        // the barrier array this lane watches (8 bytes per entry): even lanes the A columns, odd lanes the B tiles
+        const uint32_t watch_base = smem_u32(lane & 1 ? &sh->full_b[0] : &sh->full_a[0]);
         const long long my_tiles = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const uint32_t total = uint32_t(my_tiles * kblocks);
         uint32_t chunk = 0, s = 0, s_phase = 0;           // partial accumulators so far; ring position and parity
         int kb = 0, in_chunk = 0;
         bool ready = false;
         uint32_t it = 0;
+        // An iteration takes two k-blocks when they start on an even stage and lie in the same chunk (the usual
+        // case): one barrier test, one vote, one release commit and one round of loop bookkeeping for 24 MMAs.
+        // Lanes 0,1 watch the first stage, lanes 2,3 the second, lane 4 the read-out of a partial accumulator
+        // that the first k-block opens.
+        auto pairable = [&](uint32_t st, int ic, int k) { return (st & 1) == 0 && ic + 2 <= CHUNK_KB && k + 2 <= kblocks; };
         #pragma unroll 1
-        for(; it < total; it++) {
+        while(it < total) {
             const uint32_t buf = chunk & 1;
-            const bool closes_chunk = in_chunk + 1 == CHUNK_KB || kb + 1 == kblocks;
+            const bool pair = pairable(s, in_chunk, kb);
+            const int n = pair ? 2 : 1;
+            const bool closes_chunk = in_chunk + n == CHUNK_KB || kb + n == kblocks;
             if(!ready) {
-                const bool mine = lane < 2 || (lane == 2 && in_chunk == 0);
-                const uint32_t bar = lane == 2 ? acc_empty0 + 8 * buf : watch_base + 8 * s;
-                const uint32_t parity = lane == 2 ? ((chunk >> 1) & 1) ^ 1 : s_phase;
-                const int code = lane == 0 ? ST_MMA_FULL_A : (lane == 1 ? ST_MMA_FULL_B : ST_MMA_ACC);
+                const bool mine = lane < 2 || (lane < 4 && pair) || (lane == 4 && in_chunk == 0);
+                const uint32_t bar = lane == 4 ? acc_empty0 + 8 * buf : watch_base + 8 * (s + (lane >> 1));
+                const uint32_t parity = lane == 4 ? ((chunk >> 1) & 1) ^ 1 : s_phase;
+                const int code = lane == 4 ? ST_MMA_ACC : (lane & 1 ? ST_MMA_FULL_B : ST_MMA_FULL_A);
                 const bool ok = mine ? mbar_wait(bar, parity, sh, status, code) : true;
                 if(!__all_sync(0xffffffffu, ok)) break;
             }
             if(lane == 0) TC_TRACE(2, it);
             tc_fence_after();
-            // look ahead: the next k-block's barriers
-            bool peek = true;
-            {
-                const uint32_t ns = (s + 1) & (STAGES - 1);
-                const bool mine = lane < 2 || (lane == 2 && closes_chunk);
-                const uint32_t bar = lane == 2 ? acc_empty0 + 8 * (buf ^ 1) : watch_base + 8 * ns;
-                const uint32_t parity = lane == 2 ? (((chunk + 1) >> 1) & 1) ^ 1 : (ns == 0 ? s_phase ^ 1 : s_phase);
+            // the state of the next iteration, and a look at its barriers
+            const uint32_t ns = (s + n) & (STAGES - 1), nphase = ns < s ? s_phase ^ 1 : s_phase;
+            const int n_in_chunk = closes_chunk ? 0 : in_chunk + n, nkb = kb + n == kblocks ? 0 : kb + n;
+            const uint32_t nchunk = closes_chunk ? chunk + 1 : chunk;
+            bool peek = it + n < total;
+            if(peek) {
+                const bool npair = pairable(ns, n_in_chunk, nkb);
+                const bool mine = lane < 2 || (lane < 4 && npair) || (lane == 4 && n_in_chunk == 0);
+                const uint32_t bar = lane == 4 ? acc_empty0 + 8 * (nchunk & 1) : watch_base + 8 * (ns + (lane >> 1));
+                const uint32_t parity = lane == 4 ? ((nchunk >> 1) & 1) ^ 1 : nphase;
                 if(mine) peek = mbar_test(bar, parity);
             }
             const uint32_t d = tmem_base + buf * BN, a = tmem_base + A_COL_BASE + s * 64;
             const uint32_t bhi = ring_base + s * (B_STAGE_BYTES >> 4), blo = bhi + (B_TILE_BYTES >> 4);
-            uint32_t ah[4], al[4];
-            uint64_t bh[4], bl[4];
+            uint32_t ah[2][4], al[2][4];
+            uint64_t bh[2][4], bl[2][4];
             #pragma unroll
-            for(int j = 0; j < 4; j++) {
-                // K=8 step j: 8 columns further in A, 32 bytes (2 descriptor units) further in the B rows
-                ah[j] = a + 8 * j;
-                al[j] = a + 32 + 8 * j;
-                bh[j] = (uint64_t(DESC_HI) << 32) | (bhi + 2 * j);
-                bl[j] = (uint64_t(DESC_HI) << 32) | (blo + 2 * j);
-            }
+            for(int h = 0; h < 2; h++)
+                #pragma unroll
+                for(int j = 0; j < 4; j++) {
+                    // stage h of the pair; K=8 step j: 8 columns further in A, 32 bytes (2 descriptor units) further in the B rows
+                    ah[h][j] = a + h * 64 + 8 * j;
+                    al[h][j] = a + h * 64 + 32 + 8 * j;
+                    bh[h][j] = (uint64_t(DESC_HI) << 32) | (bhi + h * (B_STAGE_BYTES >> 4) + 2 * j);
+                    bl[h][j] = (uint64_t(DESC_HI) << 32) | (blo + h * (B_STAGE_BYTES >> 4) + 2 * j);
+                }
             const uint32_t accumulate = in_chunk != 0;
             if(elect_one()) {
                 TC_TRACE(6, it);
-                if(!TC_DIAG(DIAG_NO_MMA)) mma_kblock(d, ah, al, bh, bl, idesc, accumulate);
+                if(!TC_DIAG(DIAG_NO_MMA)) {
+                    mma_kblock(d, ah[0], al[0], bh[0], bl[0], idesc, accumulate);
+                    if(pair) mma_kblock(d, ah[1], al[1], bh[1], bl[1], idesc, 1u);
+                }
                 TC_TRACE(5, it);
-                if(s & 1) mma_commit(empty0 + 8 * (s >> 1));   // frees the A columns and the B tiles of this stage and the one before
+                if(pair || (s & 1)) mma_commit(empty0 + 8 * (s >> 1));   // frees the A columns and the B tiles of a pair of stages
                 if(closes_chunk) mma_commit(acc_full0 + 8 * buf);
                 TC_TRACE(3, it);
             }
             ready = __all_sync(0xffffffffu, peek);
             if(lane == 0) TC_TRACE(1, it);
-            if(closes_chunk) { chunk++; in_chunk = 0; }
-            else in_chunk++;
-            if(++kb == kblocks) kb = 0;
-            s = (s + 1) & (STAGES - 1);
-            if(s == 0) s_phase ^= 1;
+            it += n;
+            s = ns;
+            s_phase = nphase;
+            in_chunk = n_in_chunk;
+            kb = nkb;
+            chunk = nchunk;
         }
         if(lane == 0) *(volatile uint32_t *)&sh->mma_consumed = it;
     }
