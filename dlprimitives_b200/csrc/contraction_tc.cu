@@ -179,30 +179,14 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-// Shared-memory matrix descriptor for a K-major tile with 128-byte rows and the 128B swizzle:
-// 8-row groups are 1024 bytes apart (SBO), descriptor version 1 (sm_100), layout type 2.
-__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t addr)
-{
-    uint64_t d = 0;
-    d |= uint64_t((addr & 0x3FFFF) >> 4);
-    d |= uint64_t(1) << 16;             // leading byte offset (unused for swizzled K-major)
-    d |= uint64_t(1024 >> 4) << 32;     // stride byte offset
-    d |= uint64_t(1) << 46;             // version
-    d |= uint64_t(2) << 61;             // SWIZZLE_128B
-    return d;
-}
+// Shared-memory matrix descriptors (K-major tile, 128-byte rows, 128B swizzle) are put together where the
+// MMAs are issued: address >> 4 in the low word with the leading byte offset field set to 1 (unused for
+// swizzled K-major), and in the high word the stride byte offset (8-row groups 1024 bytes apart),
+// descriptor version 1 (sm_100) and layout type 2 (SWIZZLE_128B).
 // Instruction descriptor: fp32 accumulate, TF32 x TF32, both operands K-major, M = 128, N = bn.
 __host__ __device__ constexpr uint32_t instr_desc_tf32(int bn)
 {
     return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // The twelve MMAs of one k-block (four K=8 steps x three products), small terms first.  d: the
 // accumulator; ah / al: tensor-memory addresses of the hi / lo columns of A for each K=8 step;
