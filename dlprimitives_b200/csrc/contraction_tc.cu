@@ -34,6 +34,8 @@
 #include "contraction.cuh"
 #include <cstdlib>
 #include <cstdio>
+#include <mutex>
+#include <vector>
 
 namespace dlp {
 
@@ -951,10 +953,18 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packe
     const int ktab_entries = MODE == A_GATHER && L.k_pad <= 1024 && p.ktab != nullptr ? L.k_pad : 0;
     const int smem = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int((sizeof(tc::Shared) + 15) & ~size_t(15)) + ktab_entries * 8;
     const int smem_max = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int((sizeof(tc::Shared) + 15) & ~size_t(15)) + 1024 * 8;
-    static bool configured = false;   // per instantiation; the attribute is per function, set once per process
-    if(!configured) {
-        DLP_CUDA_OK(cudaFuncSetAttribute(tc::contraction_tf32x3_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
-        configured = true;
+    {
+        // The attribute belongs to the function in the current device's context: set it once per (instantiation, device).
+        static std::mutex mutex;
+        static std::vector<char> configured;          // by device ordinal
+        int dev = 0;
+        DLP_CUDA_OK(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(mutex);
+        if(size_t(dev) >= configured.size()) configured.resize(size_t(dev) + 1, 0);
+        if(!configured[dev]) {
+            DLP_CUDA_OK(cudaFuncSetAttribute(tc::contraction_tf32x3_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max));
+            configured[dev] = 1;
+        }
     }
     const long long m_tiles = ceil_div<long long>(p.rows, tc::BM);
     const int n_tiles = L.n_pad / BN;

@@ -132,14 +132,14 @@ __device__ __forceinline__ float eltwise_op(float a, float b, int op, float c0, 
     if(op == 1) return a * b * (c0 * c1);
     return fmaxf(a * c0, b * c1);
 }
-__global__ void elementwise_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ c, size_t count,
-                                   int op, float c0, float c1, int act, int vec_ok)
+// c may be a or b (in-place Elementwise): no __restrict__ and no non-coherent loads on the operands
+__global__ void elementwise_kernel(const float *a, const float *b, float *c, size_t count, int op, float c0, float c1, int act, int vec_ok)
 {
     const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, step = (size_t)gridDim.x * blockDim.x;
     if(vec_ok) {
         const size_t n4 = count / 4;
         for(size_t i = tid; i < n4; i += step) {
-            const float4 u = __ldg(reinterpret_cast<const float4 *>(a) + i), v = __ldg(reinterpret_cast<const float4 *>(b) + i);
+            const float4 u = reinterpret_cast<const float4 *>(a)[i], v = reinterpret_cast<const float4 *>(b)[i];
             float4 r;
             r.x = apply_act(eltwise_op(u.x, v.x, op, c0, c1), act);
             r.y = apply_act(eltwise_op(u.y, v.y, op, c0, c1), act);
@@ -153,14 +153,15 @@ __global__ void elementwise_kernel(const float *__restrict__ a, const float *__r
         for(size_t i = tid; i < count; i += step) c[i] = apply_act(eltwise_op(a[i], b[i], op, c0, c1), act);
 }
 
-__global__ void activation_kernel(const float *__restrict__ x, float *__restrict__ y, size_t count, int act)
+// y may be x (in place)
+__global__ void activation_kernel(const float *x, float *y, size_t count, int act)
 {
     for(size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
         y[i] = apply_act(x[i], act);
 }
 
 // one CTA per (row, inner) slice; classes strided by `inner`
-__global__ void softmax_kernel(const float *__restrict__ x, float *__restrict__ y, int classes, int inner, int log_mode)
+__global__ void softmax_kernel(const float *x, float *y, int classes, int inner, int log_mode)
 {
     __shared__ float red[32];
     const long long slice = blockIdx.x;
@@ -191,7 +192,7 @@ __global__ void softmax_kernel(const float *__restrict__ x, float *__restrict__ 
     }
 }
 
-__global__ void batchnorm_inference_kernel(const float *__restrict__ x, float *__restrict__ y, size_t count, int features, int plane,
+__global__ void batchnorm_inference_kernel(const float *x, float *y, size_t count, int features, int plane,
                                            float eps, const float *__restrict__ mean, const float *__restrict__ var,
                                            const float *__restrict__ gamma, const float *__restrict__ beta)
 {

@@ -5,8 +5,10 @@
 // of its device memory to a pool it does not control, a plugin called from inside another
 // framework's allocator callbacks, or a driver-level harness where cudaMalloc is simply not
 // permitted.  For them the scratch lives in a fixed array in the library's own device image: it is
-// part of the module, so every GPU that loads this library holds DLP_IP_STATIC_SCRATCH_BYTES of it
-// until the process exits, and nothing is ever allocated or freed at run time.
+// part of the module, so every GPU that has loaded the module holds DLP_IP_STATIC_SCRATCH_BYTES of it
+// until the process exits, and no allocation routine is ever called.  (With lazy module loading the
+// module is loaded, and the array's memory reserved, by the first address look-up on a device: the
+// first call per device belongs at start-up, while memory is still available.)
 #include "plans.cuh"
 #include <mutex>
 

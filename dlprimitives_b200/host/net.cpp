@@ -158,12 +158,8 @@ void Net::build_plan()
     steps_.clear();
     // consumers of every tensor name, by connection index
     std::map<std::string, std::vector<unsigned> > consumers;
-    std::map<std::string, unsigned> producer;
-    for(unsigned i = 0; i < connections_.size(); i++) {
+    for(unsigned i = 0; i < connections_.size(); i++)
         for(std::string const &n : connections_[i].input_names) consumers[n].push_back(i);
-        for(std::string const &n : connections_[i].output_names)
-            if(!producer.count(n)) producer[n] = i;
-    }
     std::set<std::string> outputs(outputs_.begin(), outputs_.end());
     std::vector<int> absorbed_by(connections_.size(), -1);   // Elementwise -> convolution that absorbs it
     std::vector<int> absorbs(connections_.size(), -1);
@@ -174,20 +170,22 @@ void Net::build_plan()
             Elementwise *ew = dynamic_cast<Elementwise *>(add.op.get());
             if(!ew || ew->config().op != Elementwise::Config::elementwise_sum) continue;
             if(add.input_names.size() != 2 || add.input_names[0] == add.input_names[1]) continue;
-            // the operand produced last must come from a convolution that feeds nothing else
-            int pick = -1;
-            unsigned best = 0;
-            for(int side = 0; side < 2; side++) {
-                std::string const &t = add.input_names[side];
-                auto pr = producer.find(t);
-                if(pr == producer.end()) continue;
-                if(pick < 0 || pr->second > best) { pick = side; best = pr->second; }
-            }
-            if(pick < 0) continue;
+            // The operand written last before the sum must come from a convolution that feeds nothing else.  "Written
+            // last" counts every writer of the tensor's storage (in-place operators rewrite a name, aliases share it).
+            auto last_writer = [&](std::string const &name) {
+                const std::string root = root_of(name);
+                for(int m = int(j) - 1; m >= 0; m--)
+                    for(std::string const &o : connections_[m].output_names)
+                        if(root_of(o) == root) return m;
+                return -1;
+            };
+            const int w0 = last_writer(add.input_names[0]), w1 = last_writer(add.input_names[1]);
+            if(w0 < 0 && w1 < 0) continue;
+            if(w0 == w1) continue;                         // both operands in one storage
+            const int pick = w0 > w1 ? 0 : 1;
+            const unsigned best = unsigned(std::max(w0, w1));
             std::string const &t = add.input_names[pick];
             std::string const &other = add.input_names[1 - pick];
-            auto other_pr = producer.find(other);
-            if(other_pr != producer.end() && other_pr->second >= best) continue;
             Connection &cv = connections_[best];
             Convolution2D *conv = dynamic_cast<Convolution2D *>(cv.op.get());
             if(!conv || absorbs[best] >= 0) continue;
@@ -199,15 +197,20 @@ void Net::build_plan()
             if(aliased) continue;
             if(ew->config().coeff[pick] != 1.0f) continue;
             if(std::string(conv->algo()) == "depthwise_separable") continue;
-            // nothing between the convolution and the sum may overwrite the other operand or the sum's output
+            // The fusion moves the write of the sum's output forward to the convolution's step.  So between the
+            // two nothing may write the other operand, and nothing may read or write the storage of the sum's
+            // output: with an in-place sum (output == other operand) a reader of the shortcut in between would
+            // otherwise see shortcut + branch instead of the shortcut.
             bool clobbered = false;
-            for(unsigned m = best + 1; m < j && !clobbered; m++)
+            const std::string result_root = root_of(add.output_names[0]), other_root = root_of(other);
+            for(unsigned m = best + 1; m < j && !clobbered; m++) {
                 for(std::string const &o : connections_[m].output_names)
-                    clobbered = clobbered || root_of(o) == root_of(other) || root_of(o) == root_of(add.output_names[0]);
-            // ...and nothing between them may read the sum's output tensor when that is an in-place name
-            for(unsigned m = best + 1; m < j && !clobbered; m++)
+                    clobbered = clobbered || root_of(o) == other_root || root_of(o) == result_root;
                 for(std::string const &in : connections_[m].input_names)
-                    clobbered = clobbered || (root_of(in) == root_of(add.output_names[0]) && root_of(in) != root_of(other));
+                    clobbered = clobbered || root_of(in) == result_root;
+            }
+            // the convolution itself must not read the storage it would now overwrite
+            for(std::string const &in : cv.input_names) clobbered = clobbered || root_of(in) == result_root;
             if(clobbered) continue;
             absorbs[best] = int(j);
             absorbed_by[j] = int(best);

@@ -229,7 +229,7 @@ Tensor Tensor::sub_tensor(size_t offset, Shape const &s, DataType d, bool traina
     DLPRIM_CHECK(base_bytes % size_of_data_type(d) == 0);
     t.base_ = base_;
     t.offset_ = base_bytes / size_of_data_type(d);
-    t.capacity_ = capacity_ - byte_offset;
+    t.capacity_ = bytes;       // the view's own block: the host mirror and reshape() stay inside it
     return t;
 }
 void *Tensor::host_data()

@@ -189,12 +189,17 @@ DLP_API dlp_status dlp_ip_fwd_enqueue_packed(const dlp_ip_plan *plan, const floa
  * framework's memory pool, code called from an allocator callback, a harness where cudaMalloc is
  * forbidden -- and therefore cannot hand dlp_ip_fwd_enqueue the workspace it asks for.  The scratch
  * for the packed weights is a fixed array of DLP_IP_STATIC_SCRATCH_BYTES inside the library's device
- * image; every GPU that loads the library holds that much memory until the process exits.
+ * image; every GPU on which the entry point has been called holds that much memory until the process exits.
  *   - Same arguments and result as dlp_ip_fwd_enqueue minus the workspace.
  *   - Plans whose packed weights exceed DLP_IP_STATIC_SCRATCH_BYTES are refused with
- *     DLP_INVALID_ARGUMENT and a message giving both sizes (a 2048 -> 1000 layer needs 8 MiB).
- *   - The first call on each device looks up the array's device address; make that first call before
- *     starting any stream capture.
+ *     DLP_INVALID_ARGUMENT and a message giving both sizes.  Packed weights take
+ *     2 * round_up(outputs, 128) * round_up(inputs, 32) * 4 bytes, so a 2048 -> 1000 layer needs exactly
+ *     16 MiB and sits on the limit: 2049 inputs, or 1025 outputs at 2048 inputs, are refused.
+ *   - The first call on each device looks up the array's device address.  With the CUDA runtime's lazy
+ *     module loading that look-up is also the moment the array's memory is reserved on that device, so it
+ *     can fail with an out-of-memory error if everything has been given away by then: make the first call
+ *     on each device at start-up, while memory is still available, and before starting any stream capture.
+ *     From then on the array stays resident until the process exits.
  *   - All calls on a device share the one array, which still holds the previous call's data when the
  *     next one starts (each call overwrites all of it).  Two calls whose kernels may run at the same
  *     time -- different streams without ordering, or several host threads -- race on it: order them.

@@ -132,3 +132,34 @@ def test_parameter_file_round_trip(tmp_path):
     b = hostapi.Net(net_json)
     b.load_params_file(path)
     assert np.array_equal(run_gpu(a, x, repeats=1)[0]["fc"], run_gpu(b, x, repeats=1)[0]["fc"])
+
+
+def _in_place_sum_graph(side_reader_between):
+    """conv_a(x) -> a; conv_b(a) -> t; [relu(x) -> z]; add(x, t) -> x (in place on the shortcut); [relu(x) -> z]."""
+    conv = lambda name, src, dst: {"name": name, "type": "Convolution2D", "inputs": [src], "outputs": [dst],
+                                   "options": {"channels_in": 16, "channels_out": 16, "kernel": [3, 3], "stride": [1, 1], "pad": [1, 1],
+                                               "dilate": [1, 1], "groups": 1, "bias": True, "activation": "relu"}}
+    side = {"name": "side", "type": "Activation", "inputs": ["x"], "outputs": ["z"], "options": {"activation": "relu"}}
+    add = {"name": "add", "type": "Elementwise", "inputs": ["x", "t"], "outputs": ["x"], "options": {"operation": "sum", "activation": "relu"}}
+    ops = [conv("stem", "data", "x"), conv("conv_a", "x", "a"), conv("conv_b", "a", "t")]
+    ops += [side, add] if side_reader_between else [add, side]
+    return {"inputs": [{"name": "data", "shape": [2, 16, 12, 12]}], "outputs": ["x", "z"], "operators": ops}
+
+
+@pytest.mark.parametrize("side_reader_between", [True, False])
+def test_in_place_sum_with_a_side_reader_of_the_shortcut(side_reader_between):
+    """The residual fusion writes the sum at the convolution's step.  With the sum in place on the shortcut, an
+    operator between the two that reads the shortcut must still see the shortcut: the fusion has to be refused."""
+    from dlprimitives_b200 import resnet50
+    from oracle import netrun
+    net_json = _in_place_sum_graph(side_reader_between)
+    params = resnet50.make_params(net_json, seed=11)
+    x = resnet50.make_input(net_json, seed=12)
+    net = build_gpu_net(net_json, params)
+    fused = [line for line in net.plan() if "+residual" in line]
+    assert bool(fused) == (not side_reader_between), net.plan()
+    got = run_gpu(net, x, outputs=("x", "z"), repeats=3)
+    want, _ = netrun.run(net_json, params, {"data": x}, ["x", "z"])
+    for r in got:
+        assert rel_err(r["x"], want["x"]) <= REL_TOL
+        assert rel_err(r["z"], want["z"]) <= REL_TOL
