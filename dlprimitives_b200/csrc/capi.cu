@@ -475,6 +475,14 @@ dlp_status dlp_gemm_enqueue(const dlp_gemm_plan *plan, int m, int n, int k, cons
     return launch_contraction_ffma(p, 1, 0, 0, n, (cudaStream_t)stream);
 }
 
+size_t dlp_gemm_batched_workspace(const dlp_gemm_plan *plan, int batch)
+{
+    if(!plan || !plan->use_tc || batch <= 0) return 0;
+    return tc_packed_layout(std::max(plan->d.n, 1), std::max(plan->d.k, 1)).bytes() * size_t(batch);
+}
+
+// One launch for the whole batch (src/gemm.cpp:603-638, :348-426 in the reference): the matrices are an outer index of
+// the grid.  Tensor-core plans pack every B of the batch into the workspace first (one launch as well).
 dlp_status dlp_gemm_batched_enqueue(const dlp_gemm_plan *plan, int batch, int m, int n, int k, const float *a, long long stride_a, int lda,
                                     const float *b, long long stride_b, int ldb, float *c, long long stride_c, int ldc, float beta,
                                     void *ws, size_t ws_bytes, void *stream)
@@ -482,12 +490,24 @@ dlp_status dlp_gemm_batched_enqueue(const dlp_gemm_plan *plan, int batch, int m,
     DLP_REQUIRE(plan != nullptr, "null plan");
     DLP_REQUIRE(batch >= 0, "negative batch");
     DLP_REQUIRE(plan->d.bias_mode == DLP_GEMM_NO_BIAS, "the batched product takes no bias, as in the reference");
-    for(int i = 0; i < batch; i++) {
-        dlp_status st = dlp_gemm_enqueue(plan, m, n, k, a + i * stride_a, lda, b + i * stride_b, ldb, c + i * stride_c, ldc, nullptr, beta,
-                                         ws, ws_bytes, stream);
+    if(batch == 0) return DLP_OK;
+    DLP_REQUIRE(batch <= 65535, "at most 65535 matrices per call");
+    Contraction p;
+    dlp_status st = gemm_problem(plan->d, m, n, k, a, lda, b, ldb, c, ldc, nullptr, beta, p);
+    if(st != DLP_OK) return st;
+    if(m == 0 || n == 0) return DLP_OK;
+    if(plan->use_tc && k > 0) {
+        const TcPacked L = tc_packed_layout(n, k);
+        DLP_REQUIRE(ws != nullptr && ws_bytes >= L.bytes() * size_t(batch), "workspace smaller than dlp_gemm_batched_workspace()");
+        st = tc_prepack(L, b, p.b_col_stride, p.b_k_stride, n, k, static_cast<float *>(ws), 0, (cudaStream_t)stream, batch, stride_b);
         if(st != DLP_OK) return st;
+        TcBatch bt;
+        bt.count = batch;
+        bt.a_stride = stride_a;
+        bt.y_stride = stride_c;
+        return launch_contraction_tc(p, L, static_cast<const float *>(ws), (cudaStream_t)stream, nullptr, 0, bt);
     }
-    return DLP_OK;
+    return launch_contraction_ffma(p, batch, stride_a, stride_b, 0, (cudaStream_t)stream, stride_c);
 }
 
 // ---------------------------------------------------------------------------------------------- InnerProduct

@@ -77,7 +77,8 @@ struct RowInfo {
     bool valid;
 };
 
-__device__ __forceinline__ RowInfo make_row(const Contraction &p, long long row)
+// a_off / y_off: element offsets of the matrix a batched product is working on (0 otherwise)
+__device__ __forceinline__ RowInfo make_row(const Contraction &p, long long row, long long a_off = 0, long long y_off = 0)
 {
     RowInfo r;
     r.valid = row < p.rows;
@@ -98,6 +99,8 @@ __device__ __forceinline__ RowInfo make_row(const Contraction &p, long long row)
         r.base = row * p.a_row_stride;
         r.out = p.out_mode == OUT_COL_MAJOR ? row : row * p.ldc;
     }
+    r.base += a_off;
+    r.out += y_off;
     return r;
 }
 
@@ -118,8 +121,9 @@ __device__ __forceinline__ float finish_output(const Contraction &p, const RowIn
 }
 
 // launchers (one per translation unit)
+// groups: grouped convolution (out_group_channels output channels each) or a batch of matrices (y_group_stride apart in y)
 dlp_status launch_contraction_ffma(const Contraction &p, int groups, long long a_group_stride, long long b_group_stride,
-                                   int out_group_channels, cudaStream_t stream);
+                                   int out_group_channels, cudaStream_t stream, long long y_group_stride = 0);
 
 // Pre-packed B for the tensor-core kernel: zero padded and already split into its TF32 part (hi) and
 // the remainder (lo).  It is a sequence of pipeline stages in the order (column tile, k-block of 32);
@@ -132,13 +136,24 @@ struct TcPacked {
 };
 TcPacked tc_packed_layout(int cols, int k);
 // taps > 0 packs in the A_TAPBLOCK order: packed k = ((channel block * taps + tap) * 32 + channel in block)
+// batch > 1: that many matrices b_batch_stride elements apart, packed one after the other (L.bytes() each)
 dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
-                      float *packed, int taps, cudaStream_t stream);
+                      float *packed, int taps, cudaStream_t stream, int batch = 1, long long b_batch_stride = 0);
+// A batch of equal-sized products in one launch: matrix i reads a + i * a_stride, its own packed operand and writes y + i * y_stride.
+struct TcBatch {
+    int count = 1;
+    long long a_stride = 0, y_stride = 0;
+};
 // Scratch that lets the launcher split K when the problem has too few tiles for the GPU (0: it would not split).
 size_t tc_split_scratch_bytes(long long rows, const TcPacked &L);
 // scratch may be null or short; the launcher then does not split.
 dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream, void *scratch = nullptr,
-                                 size_t scratch_bytes = 0);
+                                 size_t scratch_bytes = 0, const TcBatch &batch = TcBatch());
+
+// 1x1 stride-1 convolutions over large planes with few input channels: a kernel that moves every operand with the copy
+// engines (pointwise_tc.cu).  launch_contraction_tc hands eligible problems over by itself.
+bool pointwise_tc_eligible(const Contraction &p, const TcPacked &L);
+dlp_status launch_pointwise_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream);
 
 // Winograd F(2x2, 3x3), stride 1, padding 1 (winograd.cu).  u: the transformed filters, winograd_packed_bytes() long.
 size_t winograd_packed_bytes(int cin, int cout);

@@ -12,7 +12,7 @@ namespace {
 constexpr int TM = 64, TN = 64, TK = 16, THREADS = 256;
 
 __global__ void __launch_bounds__(THREADS)
-contraction_ffma_kernel(Contraction p, long long a_group_stride, long long b_group_stride, int out_group_channels)
+contraction_ffma_kernel(Contraction p, long long a_group_stride, long long b_group_stride, int out_group_channels, long long y_group_stride)
 {
     __shared__ float As[TK][TM + 4];
     __shared__ float Bs[TK][TN + 4];
@@ -29,6 +29,7 @@ contraction_ffma_kernel(Contraction p, long long a_group_stride, long long b_gro
 
     // loader mapping: A tile 16 k x 64 rows -> each thread 4 elements (same row index, 4 k's)
     const int a_row = tid & 63, a_k0 = tid >> 6;   // k = a_k0 + 4*i
+    const long long y_off = g * y_group_stride;     // a batch of matrices: where this one's C starts
     const RowInfo ar = make_row(p, row0 + a_row);
     // B tile 16 k x 64 cols -> thread reads k = tid & 15 (contiguous in raw weights), cols (tid >> 4) + 16*i
     const int b_k = tid & 15, b_c0 = tid >> 4;
@@ -82,7 +83,7 @@ contraction_ffma_kernel(Contraction p, long long a_group_stride, long long b_gro
     #pragma unroll
     for(int i = 0; i < 4; i++) {
         const long long row = row0 + ty * 4 + i;
-        const RowInfo r = make_row(p, row);
+        const RowInfo r = make_row(p, row, 0, y_off);
         if(!r.valid) continue;
         #pragma unroll
         for(int j = 0; j < 4; j++) {
@@ -97,13 +98,13 @@ contraction_ffma_kernel(Contraction p, long long a_group_stride, long long b_gro
 } // namespace
 
 dlp_status launch_contraction_ffma(const Contraction &p, int groups, long long a_group_stride, long long b_group_stride,
-                                   int out_group_channels, cudaStream_t stream)
+                                   int out_group_channels, cudaStream_t stream, long long y_group_stride)
 {
     if(p.rows <= 0 || p.cols <= 0 || groups <= 0) return DLP_OK;
     const long long gx = ceil_div<long long>(p.rows, TM);
     if(gx > 0x7fffffffLL) return fail(DLP_INVALID_ARGUMENT, "too many output rows for one launch");
     dim3 grid((unsigned)gx, (unsigned)ceil_div(p.cols, TN), (unsigned)groups);
-    contraction_ffma_kernel<<<grid, THREADS, 0, stream>>>(p, a_group_stride, b_group_stride, out_group_channels);
+    contraction_ffma_kernel<<<grid, THREADS, 0, stream>>>(p, a_group_stride, b_group_stride, out_group_channels, y_group_stride);
     DLP_LAUNCH_OK("contraction_ffma_kernel");
     return DLP_OK;
 }

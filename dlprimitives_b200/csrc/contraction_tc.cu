@@ -31,7 +31,7 @@
 // All mbarrier waits are bounded: a wait that gives up records a code in the device status word,
 // raises the CTA's abort flag, and every role then leaves its loop; the CTA drains its bulk copies
 // and frees its tensor memory before it returns.
-#include "contraction.cuh"
+#include "tc_device.cuh"
 #include <cstdlib>
 #include <cstdio>
 #include <mutex>
@@ -53,7 +53,6 @@ constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_PREFETCH = 2, WARP_ACC0 = 4, WARP
 constexpr int NUM_ACC_WARPS = 4, NUM_LOADER_WARPS = 8;
 constexpr int NUM_WARPS = WARP_LOAD0 + NUM_LOADER_WARPS;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
-constexpr long long WAIT_LIMIT_NS = 400ll * 1000 * 1000;
 
 // codes left in the device status word
 enum { ST_TMA_EMPTY = 101, ST_MMA_FULL_B = 102, ST_MMA_FULL_A = 103, ST_MMA_ACC = 104, ST_EPI_ACC = 105, ST_LOAD_EMPTY = 106,
@@ -78,183 +77,6 @@ struct Shared {
     uint32_t epilogue_started;   // work items of this CTA whose partial sums the accumulate warps have begun to read
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(unsigned long long *bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Barrier waits take the barrier either as a pointer or as its 32-bit shared-space address.
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, uint32_t parity) { return mbar_try_wait(smem_u32(bar), parity); }
-// non-blocking: has the phase with this parity completed?
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ long long global_ns()
-{
-    long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait by one thread.  Returns false when the CTA is aborting or the time limit ran out
-// (then it raises the abort).
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, Shared *sh, int *status, int code)
-{
-    #pragma unroll 1
-    for(int i = 0; i < 32; i++)
-        if(mbar_try_wait(bar, parity)) return true;
-    const long long t0 = global_ns();
-    #pragma unroll 1
-    for(uint32_t i = 0;; i++) {
-        if(mbar_try_wait(bar, parity)) return true;
-        __nanosleep(32);
-        if((i & 63) == 63) {
-            if(*(volatile int *)&sh->abort_flag) return false;
-            if(global_ns() - t0 > WAIT_LIMIT_NS) {
-                *(volatile int *)&sh->abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Shared *sh, int *status, int code)
-{
-    if(mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, sh, status, code);
-}
-__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code)
-{
-    return mbar_wait(smem_u32(bar), parity, sh, status, code);
-}
-// The same for a whole warp: one lane polls (32 lanes polling one barrier serialise), all get the answer.
-__device__ __forceinline__ bool warp_wait(unsigned long long *bar, uint32_t parity, Shared *sh, int *status, int code, int lane)
-{
-    int ok = 1;
-    __syncwarp();
-    if(lane == 0) ok = mbar_wait(bar, parity, sh, status, code) ? 1 : 0;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    __syncwarp();
-    return ok != 0;
-}
-
-// true in exactly one lane of a converged warp
-__device__ __forceinline__ bool elect_one()
-{
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "elect.sync _|p, 0xffffffff;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-    return pred != 0;
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Contiguous bulk copy global -> shared (both 16-byte aligned, size a multiple of 16); completion is
-// counted in bytes on the mbarrier.
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, unsigned long long *bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-
-// Shared-memory matrix descriptors (K-major tile, 128-byte rows, 128B swizzle) are put together where the
-// MMAs are issued: address >> 4 in the low word with the leading byte offset field set to 1 (unused for
-// swizzled K-major), and in the high word the stride byte offset (8-row groups 1024 bytes apart),
-// descriptor version 1 (sm_100) and layout type 2 (SWIZZLE_128B).
-// Instruction descriptor: fp32 accumulate, TF32 x TF32, both operands K-major, M = 128, N = bn.
-__host__ __device__ constexpr uint32_t instr_desc_tf32(int bn)
-{
-    return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
-}
-// The twelve MMAs of one k-block (four K=8 steps x three products), small terms first.  d: the
-// accumulator; ah / al: tensor-memory addresses of the hi / lo columns of A for each K=8 step;
-// bh / bl: shared-memory descriptors of the hi / lo tile of B for each step.  The operands come in
-// ready-made so that the caller can compute them in warp-uniform code.
-__device__ __forceinline__ void mma_kblock(uint32_t d, const uint32_t (&ah)[4], const uint32_t (&al)[4], const uint64_t (&bh)[4],
-                                           const uint64_t (&bl)[4], uint32_t idesc, uint32_t accumulate_first)
-{
-    asm volatile("{\n\t"
-                 ".reg .pred p, t;\n\t"
-                 "setp.ne.b32 p, %18, 0;\n\t"
-                 "setp.eq.b32 t, 0, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%5], %9, %17, p;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %13, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %9, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%6], %10, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], %14, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], %10, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%7], %11, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%3], %15, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%3], %11, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%8], %12, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%4], %16, %17, t;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%4], %12, %17, t;\n\t"
-                 "}"
-                 ::"r"(d), "r"(ah[0]), "r"(ah[1]), "r"(ah[2]), "r"(ah[3]), "r"(al[0]), "r"(al[1]), "r"(al[2]), "r"(al[3]),
-                   "l"(bh[0]), "l"(bh[1]), "l"(bh[2]), "l"(bh[3]), "l"(bl[0]), "l"(bl[1]), "l"(bl[2]), "l"(bl[3]),
-                   "r"(idesc), "r"(accumulate_first) : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar)   // bar: shared-space address of the mbarrier
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16])
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-                 "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                 : "r"(taddr) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[16]) { tmem_ld16(taddr, v); }
-__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&v)[32])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                   "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                   "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ bool act_is_clamp(int act) { return act == DLP_ACT_IDENTITY || act == DLP_ACT_RELU || act == DLP_ACT_RELU6; }
-__device__ __forceinline__ float2 act_clamp(int act)
-{
-    return make_float2(act == DLP_ACT_IDENTITY ? -INFINITY : 0.0f, act == DLP_ACT_RELU6 ? 6.0f : INFINITY);
-}
 // Lean store of N output columns of one row: y = clamp(acc + bias) [then clamp(y + s*residual)].
 template<int N, bool BIAS, bool RES>
 __device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const float (&res)[N], long long cs, const float *b0,
@@ -306,8 +128,12 @@ template<int BN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p, int kblocks, int n_tiles,
                           long long num_tiles, int splits, long long split_stride, int ktab_smem_entries, int *status, int diag,
-                          long long *trace)
+                          long long *trace, const TcBatch batch)
 {
+    // A batch of matrices runs as gridDim.y independent problems: blockIdx.y picks the matrix, whose A and C lie
+    // batch.a_stride / batch.y_stride elements further on and whose packed B follows the previous matrix's.
+    const long long a_off = blockIdx.y * batch.a_stride, y_off = blockIdx.y * batch.y_stride;
+    packed += (long long)blockIdx.y * (2ll * n_tiles * BN) * ((long long)kblocks * splits * BK);
 #ifdef DLP_TC_DIAGNOSTICS
     // optional timeline of CTA 0: trace[k-block or chunk][slot] = SM clock at a few points of each role
     // (bits 8.. of diag, when set, select which slots are recorded, so that a measurement can run with few probes)
@@ -379,7 +205,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 const float *src = packed + ((long long)(tile % n_tiles) * splits + part) * kblocks * (B_STAGE_BYTES / 4);
                 for(int kb = 0; kb < kblocks; kb++, it++) {
                     const int s = it % STAGES;
-                    if(!mbar_wait(&sh->empty[s >> 1], ((it / STAGES) & 1) ^ 1, sh, status, ST_TMA_EMPTY)) { live = false; break; }
+                    if(!mbar_wait(&sh->empty[s >> 1], ((it / STAGES) & 1) ^ 1, &sh->abort_flag, status, ST_TMA_EMPTY)) { live = false; break; }
                     TC_TRACE(0, it);
                     mbar_arrive_expect_tx(&sh->full_b[s], B_STAGE_BYTES);
                     bulk_load(b_ring + s * B_STAGE_BYTES, src + (long long)kb * (B_STAGE_BYTES / 4), B_STAGE_BYTES, &sh->full_b[s]);
@@ -427,7 +253,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 const uint32_t bar = lane == 4 ? acc_empty0 + 8 * buf : watch_base + 8 * (s + (lane >> 1));
                 const uint32_t parity = lane == 4 ? ((chunk >> 1) & 1) ^ 1 : s_phase;
                 const int code = lane == 4 ? ST_MMA_ACC : (lane & 1 ? ST_MMA_FULL_B : ST_MMA_FULL_A);
-                const bool ok = mine ? mbar_wait(bar, parity, sh, status, code) : true;
+                const bool ok = mine ? mbar_wait(bar, parity, &sh->abort_flag, status, code) : true;
                 if(!__all_sync(0xffffffffu, ok)) break;
             }
             if(lane == 0) TC_TRACE(2, it);
@@ -509,7 +335,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 // every 16th row of the tile (64 bytes apart in a channel plane), and its last row: touches every line
                 #pragma unroll 1
                 for(int j = 0; j <= BM / 16; j++) {
-                    const RowInfo r = make_row(p, row0 + min(16 * j, BM - 1));
+                    const RowInfo r = make_row(p, row0 + min(16 * j, BM - 1), a_off, y_off);
                     if(!r.valid) break;
                     for(int c = lane; c < BN && n0 + c < p.cols; c += 32)
                         asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + out_index(p, r, n0 + c)));
@@ -539,7 +365,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             decode_item(item, splits, tile, part);
             const int n0 = int(tile % n_tiles) * BN;
             const long long row = (tile / n_tiles) * BM + row_in_tile;
-            const RowInfo r = make_row(p, row);
+            const RowInfo r = make_row(p, row, a_off, y_off);
             const long long col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : (p.out_mode == OUT_COL_MAJOR ? p.ldc : 1ll);
             // The tile is handled 32 columns at a time: two tensor-memory loads under one wait; on the last
             // chunk the residual operand of the same columns is fetched under that wait as well.
@@ -555,7 +381,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             for(int c = 0; c < chunks_per_tile; c++, chunk++) {
                 const uint32_t buf = chunk & 1;
                 const bool first = c == 0, last = c == chunks_per_tile - 1;
-                if(!warp_wait(&sh->acc_full[buf], (chunk >> 1) & 1, sh, status, ST_EPI_ACC, lane)) { live = false; break; }
+                if(!warp_wait(&sh->acc_full[buf], (chunk >> 1) & 1, &sh->abort_flag, status, ST_EPI_ACC, lane)) { live = false; break; }
                 if(c == 0 && warp == WARP_ACC0 && lane == 0) *(volatile uint32_t *)&sh->epilogue_started = ++items_begun;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + buf * BN;
@@ -689,7 +515,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             if(c.tile != loaded_tile) {
                 loaded_tile = c.tile;
                 decode_item(c.tile, splits, loaded_row_tile, loaded_part);
-                r = make_row(p, (loaded_row_tile / n_tiles) * BM + row_in_tile);
+                r = make_row(p, (loaded_row_tile / n_tiles) * BM + row_in_tile, a_off, y_off);
                 if(TC_DIAG(DIAG_NO_A_LOADS)) r.valid = false;
                 row_mask = col_mask = 0;
                 if(MODE == A_GATHER && r.valid) {
@@ -774,7 +600,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         auto publish = [&](const Cursor &c, const float (&buf)[BK]) -> bool {
             const int s = c.it % STAGES;
             if(quad == 0 && lane == 0) TC_TRACE(6, c.it);
-            if(!warp_wait(&sh->empty[s >> 1], ((c.it / STAGES) & 1) ^ 1, sh, status, ST_LOAD_EMPTY, lane)) return false;
+            if(!warp_wait(&sh->empty[s >> 1], ((c.it / STAGES) & 1) ^ 1, &sh->abort_flag, status, ST_LOAD_EMPTY, lane)) return false;
             if(quad == 0 && lane == 0) TC_TRACE(7, c.it);
             tc_fence_after();
             const uint32_t t_hi = tmem_base + (uint32_t(quad * 32) << 16) + A_COL_BASE + s * 64;
@@ -861,9 +687,11 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
 // (see TcPacked): stage (column tile, k-block) = hi tile then lo tile, each bn rows of 32 floats with the
 // 16-byte chunks of a row permuted by the 128-byte swizzle (chunk ^ (row & 7)).
 __global__ void prepack_kernel(const float *__restrict__ b, long long col_stride, long long k_stride, int cols, int k,
-                               int n_pad, int k_pad, int bn, int taps, float *__restrict__ packed)
+                               int n_pad, int k_pad, int bn, int taps, float *__restrict__ packed, long long b_batch_stride)
 {
     const long long total = (long long)n_pad * k_pad;
+    b += blockIdx.y * b_batch_stride;           // a batch of matrices: blockIdx.y picks one, packed one after the other
+    packed += blockIdx.y * (2 * total);
     const int kblocks = k_pad / BK;
     for(long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
         const int n = int(idx / k_pad), kk = int(idx - (long long)n * k_pad);
@@ -915,12 +743,14 @@ TcPacked tc_packed_layout(int cols, int k)
 }
 
 dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
-                      float *packed, int taps, cudaStream_t stream)
+                      float *packed, int taps, cudaStream_t stream, int batch, long long b_batch_stride)
 {
     const long long total = (long long)L.n_pad * L.k_pad;
     const int threads = 256;
     const int blocks = int(std::min<long long>(ceil_div<long long>(total, threads), 8 * sm_count()));
-    tc::prepack_kernel<<<blocks, threads, 0, stream>>>(b, b_col_stride, b_k_stride, cols, k, L.n_pad, L.k_pad, L.bn, taps, packed);
+    if(batch < 1 || batch > 65535) return fail(DLP_INVALID_ARGUMENT, "a batched product takes 1 to 65535 matrices");
+    tc::prepack_kernel<<<dim3(blocks, batch), threads, 0, stream>>>(b, b_col_stride, b_k_stride, cols, k, L.n_pad, L.k_pad, L.bn, taps, packed,
+                                                                    b_batch_stride);
     DLP_LAUNCH_OK("prepack_kernel");
     return DLP_OK;
 }
@@ -947,7 +777,8 @@ int choose_splits(long long rows, const TcPacked &L)
 }
 
 template<int BN, int MODE>
-dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream, int splits, long long split_stride)
+dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream, int splits, long long split_stride,
+                     const TcBatch &batch)
 {
     // the gather table rides along in shared memory when it is at most 8 KB (1024 entries: K up to 1024)
     const int ktab_entries = MODE == A_GATHER && L.k_pad <= 1024 && p.ktab != nullptr ? L.k_pad : 0;
@@ -969,7 +800,7 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packe
     const long long m_tiles = ceil_div<long long>(p.rows, tc::BM);
     const int n_tiles = L.n_pad / BN;
     const long long num_tiles = m_tiles * n_tiles * splits;     // work items
-    const int grid = int(std::min<long long>(num_tiles, sm_count()));
+    const dim3 grid(unsigned(std::min<long long>(num_tiles, sm_count())), unsigned(batch.count));
     int diag = 0;
     long long *trace = nullptr;
 #ifdef DLP_TC_DIAGNOSTICS
@@ -985,7 +816,7 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packe
     int *status = device_status_word();
     if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
     tc::contraction_tf32x3_kernel<BN, MODE><<<grid, tc::NUM_THREADS, smem, stream>>>(packed, p, L.k_pad / tc::BK / splits, n_tiles, num_tiles,
-                                                                                     splits, split_stride, ktab_entries, status, diag, trace);
+                                                                                     splits, split_stride, ktab_entries, status, diag, trace, batch);
     DLP_LAUNCH_OK("contraction_tf32x3_kernel");
 #ifdef DLP_TC_DIAGNOSTICS
     if(trace) {
@@ -1012,11 +843,13 @@ size_t tc_split_scratch_bytes(long long rows, const TcPacked &L)
 }
 
 dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream, void *scratch,
-                                 size_t scratch_bytes)
+                                 size_t scratch_bytes, const TcBatch &batch)
 {
-    if(p.rows <= 0 || p.cols <= 0) return DLP_OK;
+    if(p.rows <= 0 || p.cols <= 0 || batch.count <= 0) return DLP_OK;
     if(reinterpret_cast<uintptr_t>(packed) % 16 != 0) return fail(DLP_INVALID_ARGUMENT, "packed weights must be 16-byte aligned");
-    int splits = choose_splits(p.rows, L);
+    if(batch.count > 65535) return fail(DLP_INVALID_ARGUMENT, "a batched product takes at most 65535 matrices");
+    int splits = batch.count > 1 ? 1 : choose_splits(p.rows, L);      // the matrices of a batch fill the GPU between them
+    if(splits == 1 && batch.count == 1 && pointwise_tc_eligible(p, L)) return launch_pointwise_tc(p, L, packed, stream);
     const long long rows_pad = ceil_div<long long>(p.rows, tc::BM) * tc::BM;
     const long long split_stride = rows_pad * L.n_pad;
     if(splits > 1 && (scratch == nullptr || scratch_bytes < size_t(splits) * split_stride * sizeof(float))) splits = 1;
@@ -1035,15 +868,15 @@ dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const 
     }
     dlp_status st = DLP_INVALID_ARGUMENT;
     switch(L.bn * 4 + p.a_mode) {
-    case 32 * 4 + A_GATHER: st = launch_bn<32, A_GATHER>(q, L, packed, stream, splits, split_stride); break;
-    case 32 * 4 + A_STRIDED: st = launch_bn<32, A_STRIDED>(q, L, packed, stream, splits, split_stride); break;
-    case 32 * 4 + A_TAPBLOCK: st = launch_bn<32, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride); break;
-    case 64 * 4 + A_GATHER: st = launch_bn<64, A_GATHER>(q, L, packed, stream, splits, split_stride); break;
-    case 64 * 4 + A_STRIDED: st = launch_bn<64, A_STRIDED>(q, L, packed, stream, splits, split_stride); break;
-    case 64 * 4 + A_TAPBLOCK: st = launch_bn<64, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride); break;
-    case 128 * 4 + A_GATHER: st = launch_bn<128, A_GATHER>(q, L, packed, stream, splits, split_stride); break;
-    case 128 * 4 + A_STRIDED: st = launch_bn<128, A_STRIDED>(q, L, packed, stream, splits, split_stride); break;
-    case 128 * 4 + A_TAPBLOCK: st = launch_bn<128, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride); break;
+    case 32 * 4 + A_GATHER: st = launch_bn<32, A_GATHER>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 32 * 4 + A_STRIDED: st = launch_bn<32, A_STRIDED>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 32 * 4 + A_TAPBLOCK: st = launch_bn<32, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 64 * 4 + A_GATHER: st = launch_bn<64, A_GATHER>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 64 * 4 + A_STRIDED: st = launch_bn<64, A_STRIDED>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 64 * 4 + A_TAPBLOCK: st = launch_bn<64, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 128 * 4 + A_GATHER: st = launch_bn<128, A_GATHER>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 128 * 4 + A_STRIDED: st = launch_bn<128, A_STRIDED>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 128 * 4 + A_TAPBLOCK: st = launch_bn<128, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride, batch); break;
     default: return fail(DLP_INVALID_ARGUMENT, "unsupported column tile");
     }
     if(st != DLP_OK || splits == 1) return st;

@@ -73,21 +73,21 @@ def test_small_resnet_against_reference_cpu_outputs(case, flags):
         assert net.activation_bytes() < net.activation_bytes(without_reuse=True)
 
 
-def test_resnet50_full_size_rows_against_reference_cpu():
-    """Config 5 at its real size on the GPU (3x224x224, full channel widths, a batch of 32); the
-    reference's CPU Net computes four of those images (it handles images independently), which keeps
-    the CPU side to about half a minute."""
+@pytest.mark.parametrize("batch,sel", [(256, [0, 100, 255]), (32, [0, 13, 31])], ids=["batch256", "batch32"])
+def test_resnet50_full_size_rows_against_reference_cpu(batch, sel):
+    """Config 5 at its real size on the GPU (3x224x224, full channel widths): the configuration's own batch of
+    256 and the per-GPU batch of an 8-GPU run (tile scheduling and the cuts along K differ with the batch).
+    The reference's CPU Net computes three of those images (it handles images independently), which keeps
+    the CPU side to about half a minute per case."""
     from oracle import bindings as ob
     if not ob.ref_available():
         pytest.skip("reference CPU build (oracle/_ref) not present")
     from dlprimitives_b200 import capi, resnet50
-    batch = 32
     net_json = resnet50.make_json(batch)
     params = resnet50.make_params(net_json, seed=0)
     x = resnet50.make_input(net_json, seed=1)
     net = build_gpu_net(net_json, params)
     got = run_gpu(net, x, repeats=2)[-1]
-    sel = [0, 13, 31]
     ref_json = resnet50.make_json(len(sel))
     ref = ob.RefNet(ref_json)
     for name in ref.param_names():
