@@ -69,6 +69,7 @@ SYMBOLS = {
     "dlp_gemm_destroy": (None, [_vp]),
     "dlp_gemm_kernel": (C.c_char_p, [_vp]),
     "dlp_gemm_workspace": (_sz, [_vp]),
+    "dlp_gemm_batched_workspace": (_sz, [_vp, _i]),
     "dlp_gemm_enqueue": (_i, [_vp, _i, _i, _i, _fp, _i, _fp, _i, _fp, _i, _fp, _f, _vp, _sz, _vp]),
     "dlp_gemm_batched_enqueue": (_i, [_vp, _i, _i, _i, _i, _fp, _ll, _i, _fp, _ll, _i, _fp, _ll, _i, _f, _vp, _sz, _vp]),
     "dlp_ip_fwd_create": (_i, [C.POINTER(IpDesc), C.POINTER(_vp)]),
@@ -247,6 +248,9 @@ class Gemm:
         ws_bytes = ws.numel() * ws.element_size() if ws is not None else 0
         check(lib().dlp_gemm_enqueue(self.h, m, n, k, _ptr(a), lda, _ptr(b), ldb, _ptr(c), ldc, _ptr(bias), float(beta), _ptr(ws),
                                      ws_bytes, _stream(stream)))
+
+    def batched_workspace(self, batch):
+        return int(lib().dlp_gemm_batched_workspace(self.h, batch))
 
     def batch_gemm(self, batch, m, n, k, a, stride_a, lda, b, stride_b, ldb, c, stride_c, ldc, beta=0.0, ws=None, stream=None):
         ws_bytes = ws.numel() * ws.element_size() if ws is not None else 0

@@ -6,6 +6,8 @@
 #include <dlprim/gpu/gemm.hpp>
 #include "host_util.hpp"
 #include <cuda_runtime.h>
+#include <algorithm>
+#include <cstring>
 
 namespace dlprim {
 using host::status_check;
@@ -177,7 +179,9 @@ public:
         d.bias_mode = bias;
         d.activation = int(act);
         d.math_mode = DLP_MATH_AUTO;
+        desc_ = d;
         status_check(dlp_gemm_create(&d, &plan_));
+        planned_[0] = M; planned_[1] = N; planned_[2] = K;
         ensure_ws(dlp_gemm_workspace(plan_));
     }
     ~GemmCuda() { dlp_gemm_destroy(plan_); }
@@ -186,6 +190,7 @@ public:
               ExecutionContext const &e) override
     {
         (void)size_of_c;   // the reference needs it for its split-K pre-scale pass; there is none here
+        if(M > planned_[0] || N > planned_[1] || K > planned_[2]) grow(M, N, K);
         float const *bp = bias ? static_cast<float const *>(bias) + bias_offset : nullptr;
         status_check(dlp_gemm_enqueue(plan_, M, N, K, static_cast<float const *>(a) + offset_a, lda, static_cast<float const *>(b) + offset_b,
                                       ldb, static_cast<float *>(c) + offset_c, ldc, bp, beta, ws_bytes_ ? ws_.device_ptr() : nullptr, ws_bytes_,
@@ -202,8 +207,97 @@ private:
             ws_bytes_ = bytes;
         }
     }
+    // Sizes at call time may exceed the ones the object was made for (the reference's kernels take any size):
+    // the scratch for the packed B grows to fit.  Releasing the old scratch waits for the device, so this is the
+    // one call that is not asynchronous; calls within the planned sizes never get here.
+    void grow(int M, int N, int K)
+    {
+        dlp_gemm_desc d;
+        d.trans_a = desc_.trans_a; d.trans_b = desc_.trans_b;
+        d.m = std::max(M, planned_[0]); d.n = std::max(N, planned_[1]); d.k = std::max(K, planned_[2]);
+        d.bias_mode = desc_.bias_mode; d.activation = desc_.activation; d.math_mode = desc_.math_mode;
+        dlp_gemm_plan *bigger = nullptr;
+        status_check(dlp_gemm_create(&d, &bigger));
+        dlp_gemm_destroy(plan_);
+        plan_ = bigger;
+        desc_ = d;
+        planned_[0] = d.m; planned_[1] = d.n; planned_[2] = d.k;
+        ensure_ws(dlp_gemm_workspace(plan_));
+    }
+    dlp_gemm_desc desc_;
+    int planned_[3];
     Context ctx_;
     dlp_gemm_plan *plan_ = nullptr;
+    Tensor ws_;
+    size_t ws_bytes_ = 0;
+};
+// The convolution behind the GEMM interface: gemm() is the call Conv2DForwardGEMM::enqueue makes in the reference.
+class ConvGemmCuda : public GEMM {
+public:
+    ConvGemmCuda(Context &ctx, int M, int K, int kernel[2], int dilate[2], int padding[2], int stride[2], int groups, int src_channels,
+                 int src_rows, int src_cols, int tgt_rows, int tgt_cols, int bias, StandardActivations act)
+        : ctx_(ctx), plane_(tgt_rows * tgt_cols), src_rows_(src_rows), src_cols_(src_cols)
+    {
+        ctx.activate();
+        DLPRIM_CHECK(bias == no_bias || bias == bias_M);            // a convolution's bias is per output channel
+        DLPRIM_CHECK(K == src_channels * kernel[0] * kernel[1]);
+        dlp_conv2d_desc d;
+        memset(&d, 0, sizeof(d));
+        d.channels_in = src_channels * groups;
+        d.channels_out = M * groups;
+        for(int i = 0; i < 2; i++) { d.kernel[i] = kernel[i]; d.stride[i] = stride[i]; d.dilate[i] = dilate[i]; d.pad[i] = padding[i]; }
+        d.groups = groups;
+        d.batch = 1;
+        d.height = src_rows;
+        d.width = src_cols;
+        d.bias = bias == bias_M;
+        d.activation = int(act);
+        d.math_mode = DLP_MATH_AUTO;
+        d.algo = "gemm";
+        status_check(dlp_conv2d_fwd_create(&d, &plan_));
+        d.algo = nullptr;
+        desc_ = d;
+        planned_batch_ = 1;
+    }
+    ~ConvGemmCuda() { dlp_conv2d_fwd_destroy(plan_); }
+    void gemm(int M, int N, int K, DeviceBuffer a, offset_type offset_a, int lda, DeviceBuffer b, offset_type offset_b, int ldb, DeviceBuffer c,
+              offset_type offset_c, int ldc, DeviceBuffer bias, offset_type bias_offset, float beta, int size_of_c,
+              ExecutionContext const &e) override
+    {
+        (void)M; (void)K; (void)lda; (void)ldb; (void)ldc; (void)size_of_c;
+        DLPRIM_CHECK(plane_ > 0 && N % plane_ == 0);
+        const int batch = N / plane_;
+        const size_t need = batch_workspace(batch);
+        if(need > ws_bytes_) {
+            ws_ = Tensor(ctx_, Shape(need), uint8_data);
+            ws_bytes_ = need;
+        }
+        float const *bp = bias ? static_cast<float const *>(bias) + bias_offset : nullptr;
+        status_check(dlp_conv2d_fwd_enqueue(plan_, static_cast<float const *>(b) + offset_b, static_cast<float const *>(a) + offset_a, bp,
+                                            static_cast<float *>(c) + offset_c, ws_bytes_ ? ws_.device_ptr() : nullptr, ws_bytes_, beta, batch,
+                                            src_rows_, src_cols_, e.stream_handle()));
+    }
+private:
+    // the plan's workspace is sized for the batch it was made with; the part that lets small batches cut K grows with the batch
+    size_t batch_workspace(int batch)
+    {
+        if(batch > planned_batch_) {
+            dlp_conv2d_desc d = desc_;
+            d.batch = batch;
+            d.algo = "gemm";
+            dlp_conv2d_plan *bigger = nullptr;
+            status_check(dlp_conv2d_fwd_create(&d, &bigger));
+            dlp_conv2d_fwd_destroy(plan_);
+            plan_ = bigger;
+            planned_batch_ = batch;
+        }
+        return dlp_conv2d_fwd_workspace(plan_);
+    }
+    Context ctx_;
+    dlp_conv2d_plan *plan_ = nullptr;
+    dlp_conv2d_desc desc_;
+    int plane_, src_rows_, src_cols_;
+    int planned_batch_ = 0;
     Tensor ws_;
     size_t ws_bytes_ = 0;
 };
@@ -213,24 +307,53 @@ std::unique_ptr<GEMM> GEMM::get_optimal_gemm(Context &ctx, DataType dtype, bool 
                                              StandardActivations act, int im2col_chan)
 {
     if(dtype != float_data) throw NotImplementedError("Only float32 GEMM is implemented");
-    DLPRIM_CHECK(im2col_chan == 0);   // the convolution path has its own entry point
+    if(im2col_chan != 0) throw NotImplementedError("a convolution GEMM comes from get_optimal_conv_gemm, which knows the geometry");
     return std::unique_ptr<GEMM>(new GemmCuda(ctx, trans_a, trans_b, M, N, K, bias, act));
 }
 
+std::unique_ptr<GEMM> GEMM::get_optimal_conv_gemm(Context &ctx, DataType dtype, GemmOpMode op_mode, bool trans_a, bool trans_b, int M, int N,
+                                                  int K, int kernel[2], int dilate[2], int padding[2], int stride[2], int groups,
+                                                  int src_channels, int src_rows, int src_cols, int tgt_rows, int tgt_cols, int bias,
+                                                  StandardActivations act, int im2col_chan)
+{
+    (void)N;
+    if(dtype != float_data) throw NotImplementedError("Only float32 GEMM is implemented");
+    if(op_mode != GemmOpMode::forward) throw NotImplementedError("only the forward convolution GEMM is implemented");
+    // the forward call of the reference: filters as given, the image operand "transposed" (src/core/conv.cpp:94-96)
+    DLPRIM_CHECK(!trans_a && trans_b);
+    DLPRIM_CHECK(im2col_chan == 0 || im2col_chan == tgt_rows * tgt_cols);
+    return std::unique_ptr<GEMM>(new ConvGemmCuda(ctx, M, K, kernel, dilate, padding, stride, groups, src_channels, src_rows, src_cols,
+                                                  tgt_rows, tgt_cols, bias, act));
+}
+
+// One launch for the batch (plus the launch that packs every B); the scratch for the packed operands is taken from and
+// returned to the stream's memory pool in stream order, so the call neither blocks nor outlives its memory.
 void GEMM::batch_sgemm(DataType dt, bool trans_a, bool trans_b, int Batch, int M, int N, int K, DeviceBuffer a, offset_type offset_a,
                        int batch_stride_a, int lda, DeviceBuffer b, offset_type offset_b, int batch_stride_b, int ldb, DeviceBuffer c,
                        offset_type offset_c, int batch_stride_c, int ldc, float beta, ExecutionContext const &e)
 {
     if(dt != float_data) throw NotImplementedError("Only float32 GEMM is implemented");
-    int dev = 0;
-    host::cuda_check(cudaGetDevice(&dev), "cudaGetDevice");
-    Context ctx(Context::cuda, 0, dev);
-    GemmCuda g(ctx, trans_a, trans_b, M, N, K, no_bias, StandardActivations::identity);
-    status_check(dlp_gemm_batched_enqueue(g.plan(), Batch, M, N, K, static_cast<float const *>(a) + offset_a, batch_stride_a, lda,
-                                          static_cast<float const *>(b) + offset_b, batch_stride_b, ldb, static_cast<float *>(c) + offset_c,
-                                          batch_stride_c, ldc, beta, g.ws_ptr(), g.ws_bytes(), e.stream_handle()));
-    // the scratch of the temporary object must outlive the kernels it was handed to
-    e.finish();
+    dlp_gemm_desc d;
+    d.trans_a = trans_a; d.trans_b = trans_b;
+    d.m = M; d.n = N; d.k = K;
+    d.bias_mode = no_bias;
+    d.activation = int(StandardActivations::identity);
+    d.math_mode = DLP_MATH_AUTO;
+    dlp_gemm_plan *plan = nullptr;
+    status_check(dlp_gemm_create(&d, &plan));
+    const size_t bytes = dlp_gemm_batched_workspace(plan, Batch);
+    cudaStream_t stream = static_cast<cudaStream_t>(e.stream_handle());
+    void *ws = nullptr;
+    cudaError_t err = bytes ? cudaMallocAsync(&ws, bytes, stream) : cudaSuccess;
+    dlp_status st = DLP_OK;
+    if(err == cudaSuccess)
+        st = dlp_gemm_batched_enqueue(plan, Batch, M, N, K, static_cast<float const *>(a) + offset_a, batch_stride_a, lda,
+                                      static_cast<float const *>(b) + offset_b, batch_stride_b, ldb, static_cast<float *>(c) + offset_c,
+                                      batch_stride_c, ldc, beta, ws, bytes, e.stream_handle());
+    if(ws) cudaFreeAsync(ws, stream);
+    dlp_gemm_destroy(plan);
+    host::cuda_check(err, "cudaMallocAsync");
+    status_check(st);
 }
 
 } // namespace gpu

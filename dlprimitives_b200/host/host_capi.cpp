@@ -5,6 +5,7 @@
 #include <dlprim/json.hpp>
 #include <dlprim/ops/conv2d.hpp>
 #include <dlprim/ops/inner_product.hpp>
+#include <dlprim/gpu/gemm.hpp>
 
 #include <cuda_runtime.h>
 #include <cstdio>
@@ -281,6 +282,54 @@ int dlp_net_step_description(const dlp_net *net, int index, char *buf, int n)
 size_t dlp_net_activation_bytes(const dlp_net *net, int without_reuse)
 {
     return without_reuse ? net->net.activation_memory_without_reuse() : net->net.activation_memory();
+}
+
+int dlp_host_gemm(int device, int trans_a, int trans_b, int plan_m, int plan_n, int plan_k, int M, int N, int K, int bias_mode, int activation,
+                  void *a, int lda, void *b, int ldb, void *c, int ldc, void *bias, float beta, void *stream)
+{
+    GUARD_BEGIN
+    Context ctx(Context::cuda, 0, device);
+    ExecutionContext e(static_cast<cudaStream_t>(stream));
+    std::unique_ptr<gpu::GEMM> g = gpu::GEMM::get_optimal_gemm(ctx, float_data, trans_a != 0, trans_b != 0, plan_m, plan_n, plan_k, bias_mode,
+                                                               StandardActivations(activation));
+    g->gemm(M, N, K, a, 0, lda, b, 0, ldb, c, 0, ldc, bias, 0, beta, M * N, e);
+    e.finish();        // the object's scratch goes away with it
+    return 0;
+    GUARD_END(1)
+}
+
+int dlp_host_batch_sgemm(int device, int trans_a, int trans_b, int batch, int M, int N, int K, void *a, int stride_a, int lda, void *b,
+                         int stride_b, int ldb, void *c, int stride_c, int ldc, float beta, void *stream)
+{
+    GUARD_BEGIN
+    Context ctx(Context::cuda, 0, device);
+    ctx.activate();
+    ExecutionContext e(static_cast<cudaStream_t>(stream));
+    gpu::GEMM::batch_sgemm(float_data, trans_a != 0, trans_b != 0, batch, M, N, K, a, 0, stride_a, lda, b, 0, stride_b, ldb, c, 0, stride_c,
+                           ldc, beta, e);
+    return 0;
+    GUARD_END(1)
+}
+
+int dlp_host_conv_gemm(int device, const int geometry[14], int channels_out_per_group, int batch, int with_bias, int activation, void *filters,
+                       void *x, void *y, void *bias, float factor, void *stream)
+{
+    GUARD_BEGIN
+    Context ctx(Context::cuda, 0, device);
+    ExecutionContext e(static_cast<cudaStream_t>(stream));
+    int kernel[2] = { geometry[0], geometry[1] }, dilate[2] = { geometry[2], geometry[3] }, pad[2] = { geometry[4], geometry[5] },
+        stride[2] = { geometry[6], geometry[7] };
+    const int groups = geometry[8], src_channels = geometry[9], src_rows = geometry[10], src_cols = geometry[11], tgt_rows = geometry[12],
+              tgt_cols = geometry[13];
+    const int M = channels_out_per_group, N = tgt_rows * tgt_cols * batch, K = src_channels * kernel[0] * kernel[1];
+    std::unique_ptr<gpu::GEMM> g = gpu::GEMM::get_optimal_conv_gemm(ctx, float_data, GemmOpMode::forward, false, true, M, N, K, kernel, dilate, pad,
+                                                                    stride, groups, src_channels, src_rows, src_cols, tgt_rows, tgt_cols,
+                                                                    with_bias ? gpu::GEMM::bias_M : gpu::GEMM::no_bias,
+                                                                    StandardActivations(activation), tgt_rows * tgt_cols);
+    g->gemm(M, N, K, filters, 0, K, x, 0, K, y, 0, tgt_rows * tgt_cols, with_bias ? bias : nullptr, 0, factor, M * groups * N, e);
+    e.finish();
+    return 0;
+    GUARD_END(1)
 }
 
 } // extern "C"

@@ -46,6 +46,9 @@ SYMBOLS = {
     "dlp_net_num_steps": (_i, [_vp]),
     "dlp_net_step_description": (_i, [_vp, _i, C.c_char_p, _i]),
     "dlp_net_activation_bytes": (_sz, [_vp, _i]),
+    "dlp_host_gemm": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp, _i, _vp, C.c_float, _vp]),
+    "dlp_host_batch_sgemm": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _i, _i, C.c_float, _vp]),
+    "dlp_host_conv_gemm": (_i, [_i, _ip, _i, _i, _i, _i, _vp, _vp, _vp, _vp, C.c_float, _vp]),
 }
 _lib = None
 
@@ -256,3 +259,35 @@ def _host_ptr(t):
         return t.ctypes.data, t.size
     assert not t.is_cuda and t.is_contiguous()
     return t.data_ptr(), t.numel()
+
+
+def _dptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def gemm(trans_a, trans_b, m, n, k, a, lda, b, ldb, c, ldc, bias=None, bias_mode=0, activation="identity", beta=0.0, planned=None,
+         stream=None, device=0):
+    """gpu::GEMM::get_optimal_gemm(...)->gemm(...) on device tensors; planned = (M, N, K) the object is made for."""
+    pm, pn, pk = planned or (m, n, k)
+    if lib().dlp_host_gemm(device, int(trans_a), int(trans_b), pm, pn, pk, m, n, k, bias_mode, capi._act(activation), _dptr(a), lda, _dptr(b),
+                           ldb, _dptr(c), ldc, _dptr(bias), float(beta), _stream(stream)):
+        _fail()
+
+
+def batch_sgemm(trans_a, trans_b, batch, m, n, k, a, stride_a, lda, b, stride_b, ldb, c, stride_c, ldc, beta=0.0, stream=None, device=0):
+    """gpu::GEMM::batch_sgemm on device tensors (asynchronous on the stream)."""
+    if lib().dlp_host_batch_sgemm(device, int(trans_a), int(trans_b), batch, m, n, k, _dptr(a), stride_a, lda, _dptr(b), stride_b, ldb,
+                                  _dptr(c), stride_c, ldc, float(beta), _stream(stream)):
+        _fail()
+
+
+def conv_gemm(x, w, bias, y, stride=1, pad=0, dilate=1, groups=1, activation="identity", factor=0.0, stream=None, device=0):
+    """gpu::GEMM::get_optimal_conv_gemm(forward)->gemm(filters, x, y) the way the reference's Conv2DForwardGEMM calls it."""
+    pair = lambda v: [v, v] if isinstance(v, int) else list(v)
+    n, cin, h, wd = x.shape
+    cout, cin_g, kh, kw = w.shape
+    geometry = [kh, kw] + pair(dilate) + pair(pad) + pair(stride) + [groups, cin_g, h, wd, y.shape[2], y.shape[3]]
+    arr = (C.c_int * 14)(*geometry)
+    if lib().dlp_host_conv_gemm(device, arr, cout // groups, n, int(bias is not None), capi._act(activation), _dptr(w), _dptr(x), _dptr(y),
+                                _dptr(bias), float(factor), _stream(stream)):
+        _fail()

@@ -151,7 +151,9 @@ DLP_API size_t dlp_gemm_workspace(const dlp_gemm_plan *plan);
 DLP_API dlp_status dlp_gemm_enqueue(const dlp_gemm_plan *plan, int m, int n, int k, const float *a, int lda, const float *b,
                                     int ldb, float *c, int ldc, const float *bias, float beta, void *ws, size_t ws_bytes,
                                     void *stream);
-/* GEMM::batch_sgemm: `batch` independent products with element strides between matrices. */
+/* GEMM::batch_sgemm (src/gemm.cpp:603-638): `batch` independent products with element strides between matrices, in one
+ * launch (plus one launch that packs every B for tensor-core plans).  ws: dlp_gemm_batched_workspace(plan, batch) bytes. */
+DLP_API size_t dlp_gemm_batched_workspace(const dlp_gemm_plan *plan, int batch);
 DLP_API dlp_status dlp_gemm_batched_enqueue(const dlp_gemm_plan *plan, int batch, int m, int n, int k, const float *a,
                                             long long stride_a, int lda, const float *b, long long stride_b, int ldb, float *c,
                                             long long stride_c, int ldc, float beta, void *ws, size_t ws_bytes, void *stream);

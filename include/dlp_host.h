@@ -72,6 +72,19 @@ DLP_HOST_API int dlp_net_num_steps(const dlp_net *net);
 DLP_HOST_API int dlp_net_step_description(const dlp_net *net, int index, char *buf, int buf_size);
 DLP_HOST_API size_t dlp_net_activation_bytes(const dlp_net *net, int without_reuse);
 
+/* ---- gpu::GEMM (include/dlprim/gpu/gemm.hpp), on device buffers; each call makes the object, runs it and lets it go ---- */
+/* GEMM::get_optimal_gemm(...)->gemm(...): C[M,N] = beta*C + act(op(A)*op(B) + bias); the object is made for (plan_m, plan_n,
+ * plan_k) and called with (M, N, K), which may be larger */
+DLP_HOST_API int dlp_host_gemm(int device, int trans_a, int trans_b, int plan_m, int plan_n, int plan_k, int M, int N, int K, int bias_mode,
+                               int activation, void *a, int lda, void *b, int ldb, void *c, int ldc, void *bias, float beta, void *stream);
+/* GEMM::batch_sgemm: asynchronous on the stream */
+DLP_HOST_API int dlp_host_batch_sgemm(int device, int trans_a, int trans_b, int batch, int M, int N, int K, void *a, int stride_a, int lda,
+                                      void *b, int stride_b, int ldb, void *c, int stride_c, int ldc, float beta, void *stream);
+/* GEMM::get_optimal_conv_gemm(forward)->gemm(...) called the way the reference's Conv2DForwardGEMM calls it: geometry[] =
+ * kernel h,w, dilate h,w, pad h,w, stride h,w, groups, src_channels (per group), src_rows, src_cols, tgt_rows, tgt_cols */
+DLP_HOST_API int dlp_host_conv_gemm(int device, const int geometry[14], int channels_out_per_group, int batch, int with_bias, int activation,
+                                    void *filters, void *x, void *y, void *bias, float factor, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -36,6 +36,16 @@ namespace gpu {
         static std::unique_ptr<GEMM> get_optimal_gemm(Context &ctx, DataType dtype, bool trans_a, bool trans_b, int M, int N, int K,
                                                       int bias = 0, StandardActivations act = StandardActivations::identity,
                                                       int im2col_chan = 0);
+
+        /// The convolution as a GEMM with implicit im2col (include/dlprim/gpu/gemm.hpp:70-80, src/gemm.cpp:581-601 in the
+        /// reference).  gemm() is then called the way Conv2DForwardGEMM calls it (src/core/conv.cpp:51-80): a = the
+        /// filters [M = Cout/groups, K], b = the NCHW input, c = the NCHW output with N = batch * tgt_rows * tgt_cols
+        /// columns, bias per M, beta = the output's factor.  Only GemmOpMode::forward is implemented.
+        static std::unique_ptr<GEMM> get_optimal_conv_gemm(Context &ctx, DataType dtype, GemmOpMode op_mode, bool trans_a, bool trans_b,
+                                                           int M, int N, int K, int kernel[2], int dilate[2], int padding[2],
+                                                           int stride[2], int groups, int src_channels, int src_rows, int src_cols,
+                                                           int tgt_rows, int tgt_cols, int bias = 0,
+                                                           StandardActivations act = StandardActivations::identity, int im2col_chan = 0);
     };
 
 } // namespace gpu

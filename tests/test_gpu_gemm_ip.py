@@ -9,29 +9,103 @@ from gpu_util import DEV, REL_TOL, kaiming, rel_err, to_dev
 pytestmark = pytest.mark.gpu
 
 
+# the reference's GEMM test shapes (tests/test_gemm.cpp:104-123) and a few ragged ones of our own
+REFERENCE_GEMM_SHAPES = [(1, 1, 1), (8, 1, 8), (1, 8, 8), (8, 8, 1), (31, 16, 31), (16, 31, 31), (31, 31, 16), (512, 512, 512),
+                         (1024, 1024, 1024), (1025, 1025, 1025), (2048, 2048, 2048), (2049, 2049, 2049), (64, 2048, 64), (2048, 64, 2048),
+                         (2048, 2048, 64), (2048, 64, 64), (64, 2048, 2048), (64, 64, 2048)]
+OWN_GEMM_SHAPES = [(129, 65, 33), (1025, 31, 65), (31, 1025, 129), (64, 2049, 64), (2049, 64, 31), (5, 1000, 2048), (256, 1000, 512),
+                   (1, 513, 700), (300, 1, 257)]
+
+
+def _integer_matrices(gen, count, rows, cols):
+    """Integer-valued fp32 matrices (N(-5, 5) rounded, as in tests/test_gemm.cpp:35-38): every product and sum of the
+    test is an integer far below 2^24, so any order of summation gives the same fp32 result and equality is exact."""
+    return torch.round(torch.randn(count, rows, cols, device=DEV, generator=gen) * 5 - 5)
+
+
 @pytest.mark.parametrize("math_mode", [0, 1], ids=["auto", "ffma"])
 def test_gemm_integer_exact_sweep(math_mode):
-    """The reference's GEMM test (tests/test_gemm.cpp:10-144): integer-valued inputs, so the result
-    must be bit-exact whatever the order of summation; shapes with 1, 31, 1025, 2049 and skinny
-    ones; all four transpositions; beta 0 and 2."""
+    """The reference's GEMM test (tests/test_gemm.cpp:10-144): its 18 shapes plus ragged ones, all four transpositions,
+    beta 0 and 2, batch none / 1 / 5 (batch_sgemm), integer-valued inputs, so the result must be bit-exact.  The
+    expected product is computed in float64 (exact for these magnitudes) on the same device; a few small shapes are
+    also checked against numpy's int64 product."""
     from dlprimitives_b200 import capi
-    rng = np.random.default_rng(9)
-    shapes = [(1, 1, 1), (31, 31, 31), (64, 64, 64), (128, 128, 128), (129, 65, 33), (1025, 31, 65), (31, 1025, 129), (64, 2049, 64),
-              (2049, 64, 31), (5, 1000, 2048), (256, 1000, 512), (1, 513, 700), (300, 1, 257)]
-    for M, N, K in shapes:
-        for ta in (False, True):
-            for tb in (False, True):
-                for beta in (0.0, 2.0):
-                    a = np.round(rng.normal(-5, 5, size=(K, M) if ta else (M, K))).astype(np.float32)
-                    b = np.round(rng.normal(-5, 5, size=(N, K) if tb else (K, N))).astype(np.float32)
-                    c0 = np.round(rng.normal(-5, 5, size=(M, N))).astype(np.float32)
-                    want = (a.T if ta else a).astype(np.int64) @ (b.T if tb else b).astype(np.int64) + int(beta) * c0.astype(np.int64)
-                    g = capi.Gemm(ta, tb, M, N, K, math_mode=math_mode)
-                    c = to_dev(c0)
-                    ws = torch.empty(max(g.workspace(), 16), dtype=torch.uint8, device=DEV)
-                    g.gemm(M, N, K, to_dev(a), a.shape[1], to_dev(b), b.shape[1], c, N, beta=beta, ws=ws)
-                    got = c.cpu().numpy()
-                    assert np.array_equal(got.astype(np.int64), want), (M, N, K, ta, tb, beta, g.kernel())
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(9)
+    cases = 0
+    for M, N, K in REFERENCE_GEMM_SHAPES + OWN_GEMM_SHAPES:
+        big = M * N * K > 2 ** 28
+        if math_mode == 1 and M * N * K > 2 ** 31:
+            continue                                # the plain-FMA kernel on 2048^3 and up: covered by the 1024/1025 cubes
+        for batch in (0, 1, 5):
+            if big and batch == 5 and (M, N, K) not in ((2048, 2048, 2048),):
+                continue                            # one large batched case is enough GPU memory and time
+            for ta in (False, True):
+                for tb in (False, True):
+                    for beta in (0.0, 2.0):
+                        nb = max(batch, 1)
+                        a = _integer_matrices(gen, nb, K if ta else M, M if ta else K)
+                        b = _integer_matrices(gen, nb, N if tb else K, K if tb else N)
+                        c = _integer_matrices(gen, nb, M, N)
+                        opa = a.transpose(1, 2) if ta else a
+                        opb = b.transpose(1, 2) if tb else b
+                        c0 = c.clone()
+                        want = torch.bmm(opa.double(), opb.double()) + beta * c0.double()
+                        g = capi.Gemm(ta, tb, M, N, K, math_mode=math_mode)
+                        if batch == 0:
+                            ws = torch.empty(max(g.workspace(), 16), dtype=torch.uint8, device=DEV)
+                            g.gemm(M, N, K, a[0], a.shape[2], b[0], b.shape[2], c[0], N, beta=beta, ws=ws)
+                        else:
+                            ws = torch.empty(max(g.batched_workspace(nb), 16), dtype=torch.uint8, device=DEV)
+                            g.batch_gemm(nb, M, N, K, a, a.shape[1] * a.shape[2], a.shape[2], b, b.shape[1] * b.shape[2], b.shape[2], c, M * N, N,
+                                         beta=beta, ws=ws)
+                        assert torch.equal(c.double(), want), (M, N, K, batch, ta, tb, beta, g.kernel())
+                        if M * N * K <= 31 ** 3:
+                            ref = opa.cpu().numpy().astype(np.int64) @ opb.cpu().numpy().astype(np.int64) + int(beta) * c0.cpu().numpy().astype(np.int64)
+                            assert np.array_equal(c.cpu().numpy().astype(np.int64), ref)
+                        cases += 1
+    assert cases >= 500
+    assert capi.device_status() == 0
+
+
+def test_host_gemm_interface():
+    """The C++ gpu::GEMM class: an object made for small sizes called with larger ones (its scratch grows), batch_sgemm
+    (asynchronous, scratch from the stream's pool) in all transpositions, and the convolution GEMM factory called the
+    way the reference's Conv2DForwardGEMM calls it."""
+    from dlprimitives_b200 import capi, hostapi
+    from oracle import bindings as ob
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(21)
+    M, N, K = 300, 520, 200
+    a = _integer_matrices(gen, 1, M, K)[0]
+    b = _integer_matrices(gen, 1, K, N)[0]
+    c = torch.zeros(M, N, device=DEV)
+    hostapi.gemm(False, False, M, N, K, a, K, b, N, c, N, planned=(64, 64, 64))
+    assert torch.equal(c.double(), a.double() @ b.double())
+    stream = torch.cuda.Stream()
+    for ta in (False, True):
+        for tb in (False, True):
+            B, m, n, k = 5, 96, 200, 130
+            a = _integer_matrices(gen, B, k if ta else m, m if ta else k)
+            b = _integer_matrices(gen, B, n if tb else k, k if tb else n)
+            c = _integer_matrices(gen, B, m, n)
+            want = torch.bmm((a.transpose(1, 2) if ta else a).double(), (b.transpose(1, 2) if tb else b).double()) + 2.0 * c.double()
+            torch.cuda.synchronize()
+            with torch.cuda.stream(stream):
+                hostapi.batch_sgemm(ta, tb, B, m, n, k, a, a.shape[1] * a.shape[2], a.shape[2], b, b.shape[1] * b.shape[2], b.shape[2], c,
+                                    m * n, n, beta=2.0, stream=stream)
+            stream.synchronize()
+            assert torch.equal(c.double(), want), (ta, tb)
+    rng = np.random.default_rng(22)
+    for groups, k, stride, pad in ((1, 3, 1, 1), (2, 3, 2, 1), (1, 1, 1, 0)):
+        x = rng.standard_normal((3, 16, 20, 18), dtype=np.float32)
+        w = kaiming(rng, (24, 16 // groups, k, k))
+        bias = rng.uniform(-1, 1, 24).astype(np.float32)
+        want = ob.conv2d(x, w, bias, stride=stride, pad=pad, groups=groups, activation="relu")
+        y0 = rng.standard_normal(want.shape).astype(np.float32)
+        y = to_dev(y0)
+        hostapi.conv_gemm(to_dev(x), to_dev(w), to_dev(bias), y, stride=stride, pad=pad, groups=groups, activation="relu", factor=0.5)
+        assert rel_err(y.cpu().numpy(), 0.5 * y0 + want) <= REL_TOL, (groups, k, stride, pad)
     assert capi.device_status() == 0
 
 
