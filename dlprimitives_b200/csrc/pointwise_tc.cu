@@ -17,8 +17,9 @@
 //       - result: the epilogue warps read the accumulator from tensor memory, add bias / activation / residual,
 //         write the finished 128 x 32 block into the same epilogue buffer and one thread stores it with a
 //         tensor-map copy, which clips the pixels beyond the image and the channels beyond the tensor.
-//   * Roles: warp 0 A copies, warp 1 MMA issue, warp 2 residual copies, warp 3 B copies, warps 4-7 epilogue,
-//     warps 8-15 converters (two groups taking k-blocks in turn).
+//   * Roles (20 warps): warp 0 A copies, warp 1 MMA issue, warp 2 residual copies, warp 3 B copies, warps 8-15 converters
+//     (two groups taking k-blocks in turn), warps 4-7 and 16-19 two sets of epilogue warps that take the 32-channel groups of a tile in turn (the tile's
+//     time is its epilogue: each set has its own block barrier, its own storing thread and its own stores in flight).
 //   * Every wait is bounded (device status word + abort flag, as in the general kernel); each copy-issuing
 //     thread waits for its own copies before it leaves, and tensor memory is freed on every path.
 //
@@ -37,35 +38,38 @@ using namespace tc;
 
 constexpr int BM = 128, BK = 32;
 constexpr int T_STAGES = 4;                 // tensor-memory ring of A (and the B ring when the weights stream)
-constexpr int S_STAGES = 3;                 // shared-memory ring the tensor-map copies of A land in
-constexpr int E_BUFS = 3;                   // epilogue buffers (residual in, result out): 128 pixels x 32 channels
-constexpr int B_REGION_BYTES = 128 * 1024;  // resident weights or the B ring
+// Shared memory is shared out per launch: the weights take what they need (resident: the column tile's whole K, at most
+// 128 KB; streaming: four stages), the rest goes to the ring the tensor-map copies of A land in (s_stages x 16 KB) and
+// to the epilogue buffers (e_bufs x 16 KB: residual in, result out, 128 pixels x 32 channels each).
+constexpr int MAX_S_STAGES = 6, MAX_E_BUFS = 8;
+constexpr int MAX_B_BYTES = 128 * 1024;
 constexpr int MAX_B_STAGES = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 4;
 constexpr int E_BUF_BYTES = BM * 32 * 4;
 constexpr int A_COL_BASE = 256, TMEM_COLS = 512;
-constexpr int WARP_A = 0, WARP_MMA = 1, WARP_RES = 2, WARP_B = 3, WARP_ACC0 = 4, WARP_CONV0 = 8;
-constexpr int NUM_WARPS = 16, NUM_THREADS = NUM_WARPS * 32;
-constexpr int SMEM_BYTES = 1024 + B_REGION_BYTES + S_STAGES * A_STAGE_BYTES + E_BUFS * E_BUF_BYTES + 512;
+constexpr int WARP_A = 0, WARP_MMA = 1, WARP_RES = 2, WARP_B = 3, WARP_ACC0 = 4, WARP_CONV0 = 8, WARP_ACC1 = 16;
+constexpr int NUM_WARPS = 20, NUM_THREADS = NUM_WARPS * 32;
+constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int SMEM_FIXED = 1024 + 1024;     // alignment slack + the barrier block
 
 // codes left in the device status word
 enum { ST_A_EMPTY = 201, ST_B_EMPTY = 202, ST_RES_EMPTY = 203, ST_CONV_FULL = 204, ST_CONV_EMPTY = 205, ST_MMA_A = 206, ST_MMA_B = 207,
        ST_MMA_ACC = 208, ST_EPI_ACC = 209, ST_EPI_BUF = 210, ST_DRAIN = 211 };
 
 struct Shared {
-    unsigned long long sa_full[S_STAGES];      // a tensor-map copy of A landed in the shared-memory ring
-    unsigned long long sa_empty[S_STAGES];     // ... and the four converter warps of its k-block have read it
+    unsigned long long sa_full[MAX_S_STAGES];  // a tensor-map copy of A landed in the shared-memory ring
+    unsigned long long sa_empty[MAX_S_STAGES]; // ... and the four converter warps of its k-block have read it
     unsigned long long full_a[T_STAGES];       // the k-block's hi/lo columns are written to tensor memory (4 converter warps)
     unsigned long long full_b[MAX_B_STAGES];   // a B stage landed
     unsigned long long empty[T_STAGES];        // the MMAs of a k-block retired: its tensor-memory columns (and B stage) are free
     unsigned long long acc_full[2], acc_empty[2];
-    unsigned long long e_full[E_BUFS];         // residual operand landed in an epilogue buffer
-    unsigned long long e_empty[E_BUFS];        // the store of an epilogue buffer has read it
+    unsigned long long e_full[MAX_E_BUFS];     // residual operand landed in an epilogue buffer
+    unsigned long long e_empty[MAX_E_BUFS];    // the store of an epilogue buffer has read it
     unsigned long long drain;
     uint32_t tmem_base;
     int abort_flag;
 };
-static_assert(sizeof(Shared) <= 512, "barrier block");
+static_assert(sizeof(Shared) <= 1024, "barrier block");
 
 struct Params {
     int plane;              // pixels per image (H*W)
@@ -75,6 +79,8 @@ struct Params {
     int n_tiles;            // column tiles
     long long num_items;    // images * tiles_per_image * n_tiles
     int resident;           // the weights of a CTA's column tile are copied once and stay in shared memory
+    int b_bytes;            // shared memory set aside for the weights
+    int s_stages, e_bufs;   // depth of the A ring and number of epilogue buffers
     const float *bias;      // per output channel or null
     int act, post_act;
     int has_res;
@@ -94,12 +100,12 @@ __device__ __forceinline__ Item decode(long long item, const Params &q)
     return w;
 }
 
-// Barrier 1 of the CTA, for the 128 epilogue threads, with an AND vote riding on it.
-__device__ __forceinline__ bool epilogue_barrier_all(bool ok)
+// Barrier 1 + set of the CTA, for the 128 threads of a set of epilogue warps, with an AND vote riding on it.
+__device__ __forceinline__ bool epilogue_barrier_all(bool ok, int set)
 {
     uint32_t r;
-    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(r) : "r"(uint32_t(ok)) : "memory");
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(r) : "r"(uint32_t(ok)), "r"(1 + set) : "memory");
     return r != 0;
 }
 
@@ -125,13 +131,13 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
     unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int B_TILE_BYTES = BN * BK * 4;
     constexpr int B_STAGE_BYTES = 2 * B_TILE_BYTES;              // hi tile, then lo tile
-    constexpr int B_STAGES = B_REGION_BYTES / B_STAGE_BYTES;     // 4 / 8 / 16
-    static_assert(B_STAGES <= MAX_B_STAGES, "barrier array");
+    static_assert(MAX_B_BYTES / B_STAGE_BYTES <= MAX_B_STAGES, "barrier array");
     constexpr int GROUPS = BN / 32;
-    unsigned char *b_region = smem;
-    unsigned char *a_ring = smem + B_REGION_BYTES;
-    float *e_bufs = reinterpret_cast<float *>(smem + B_REGION_BYTES + S_STAGES * A_STAGE_BYTES);
-    Shared *sh = reinterpret_cast<Shared *>(smem + B_REGION_BYTES + S_STAGES * A_STAGE_BYTES + E_BUFS * E_BUF_BYTES);
+    const int S_STAGES = q.s_stages, E_BUFS = q.e_bufs;
+    Shared *sh = reinterpret_cast<Shared *>(smem);
+    unsigned char *b_region = smem + 1024;
+    unsigned char *a_ring = b_region + q.b_bytes;
+    float *e_bufs = reinterpret_cast<float *>(a_ring + S_STAGES * A_STAGE_BYTES);
     int *abort_flag = &sh->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,11 +145,11 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
     const long long my_items = blockIdx.x < q.num_items ? (q.num_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
     if(threadIdx.x == 0) {
-        for(int s = 0; s < S_STAGES; s++) { mbar_init(&sh->sa_full[s], 1); mbar_init(&sh->sa_empty[s], 4); }
+        for(int s = 0; s < MAX_S_STAGES; s++) { mbar_init(&sh->sa_full[s], 1); mbar_init(&sh->sa_empty[s], 4); }
         for(int s = 0; s < T_STAGES; s++) { mbar_init(&sh->full_a[s], 4); mbar_init(&sh->empty[s], 1); }
         for(int s = 0; s < MAX_B_STAGES; s++) mbar_init(&sh->full_b[s], 1);
-        for(int a = 0; a < 2; a++) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], 4); }
-        for(int e = 0; e < E_BUFS; e++) { mbar_init(&sh->e_full[e], 1); mbar_init(&sh->e_empty[e], 1); }
+        for(int a = 0; a < 2; a++) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], 4 * (GROUPS > 1 ? 2 : 1)); }
+        for(int e = 0; e < MAX_E_BUFS; e++) { mbar_init(&sh->e_full[e], 1); mbar_init(&sh->e_empty[e], 1); }
         mbar_init(&sh->drain, 1);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -265,14 +271,17 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
             }
         }
     }
-    else if(warp < WARP_CONV0) {
+    else if(warp < WARP_CONV0 || warp >= WARP_ACC1) {
         // ------------------------------------------------------------------ epilogue
         const int quad = warp & 3;
+        const int set = warp >= WARP_ACC1 ? 1 : 0;                 // which of the two sets of epilogue warps
+        constexpr int SETS = GROUPS > 1 ? 2 : 1;
+        if(set >= SETS) goto teardown;                            // a 32-channel tile has one group: the second set has no work
         const int row = quad * 32 + lane;
         const float2 clamp = act_clamp(q.act), post_clamp = act_clamp(q.post_act);
         const bool lean = act_is_clamp(q.act) && act_is_clamp(q.post_act);
-        const bool storer = warp == WARP_ACC0 && lane == 0;
-        uint32_t j = 0;
+        const bool storer = (warp == WARP_ACC0 || warp == WARP_ACC1) && lane == 0;
+        const bool release_at_once = q.has_res || E_BUFS < 2 * SETS;
         bool live = true;
         long long i = 0;
         for(long long item = blockIdx.x; item < q.num_items && live; item += gridDim.x, i++) {
@@ -285,7 +294,8 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
             tc_fence_after();
             const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + buf * BN;
             #pragma unroll 1
-            for(int g = 0; g < GROUPS; g++, j++) {
+            for(int g = set; g < GROUPS; g += SETS) {
+                const uint32_t j = uint32_t(i) * GROUPS + g;        // the group's number in the CTA's sequence: picks its buffer
                 const int e = j % E_BUFS;
                 const int col0 = w.n_tile * BN + g * 32;
                 if(ok) {
@@ -298,7 +308,8 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
                     ok = q.has_res ? warp_wait(&sh->e_full[e], (j / E_BUFS) & 1, abort_flag, status, ST_EPI_BUF, lane)
                                    : warp_wait(&sh->e_empty[e], ((j / E_BUFS) & 1) ^ 1, abort_flag, status, ST_EPI_BUF, lane);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if(g == GROUPS - 1) {
+                    if(g + SETS >= GROUPS) {
+                        // this warp's last read of the accumulator
                         tc_fence_before();
                         __syncwarp();
                         if(lane == 0) mbar_arrive(&sh->acc_empty[buf]);
@@ -329,13 +340,21 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
                     }
                 }
                 // the four epilogue warps meet: the block is complete (or somebody gave up)
-                if(!epilogue_barrier_all(ok)) { live = false; break; }
+                if(!epilogue_barrier_all(ok, set)) { live = false; break; }
                 if(storer) {
                     tma_store_3d(&tm_y, w.pix0, col0, w.b, e_bufs + e * (E_BUF_BYTES / 4));
                     bulk_commit_group();
-                    // every store but this one has read its buffer: hand the previous group's buffer back
-                    bulk_wait_group_read<1>();
-                    if(j > 0) mbar_arrive(&sh->e_empty[(j - 1) % E_BUFS]);
+                    if(release_at_once) {
+                        // once the store has read the buffer it can take the residual operand of a later group: the sooner the
+                        // copy thread learns of it, the further ahead of the epilogue its copies run
+                        bulk_wait_group_read<0>();
+                        mbar_arrive(&sh->e_empty[e]);
+                    }
+                    else {
+                        // nobody is waiting to fill the buffer: let this store read on and hand back the set's previous one
+                        bulk_wait_group_read<1>();
+                        if(j >= uint32_t(SETS)) mbar_arrive(&sh->e_empty[(j - SETS) % E_BUFS]);
+                    }
                 }
             }
         }
@@ -381,6 +400,7 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
     }
 
     // ---------------------------------------------------------------------- teardown
+teardown:
     tc_fence_before();
     __syncthreads();
     if(*(volatile int *)abort_flag) {
@@ -446,7 +466,7 @@ static dlp_status launch_bn(const CUtensorMap &tx, const CUtensorMap &ty, const 
         std::lock_guard<std::mutex> lock(mutex);
         if(size_t(dev) >= configured.size()) configured.resize(size_t(dev) + 1, 0);
         if(!configured[dev]) {
-            DLP_CUDA_OK(cudaFuncSetAttribute(pointwise_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+            DLP_CUDA_OK(cudaFuncSetAttribute(pointwise_tf32x3_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
             configured[dev] = 1;
         }
     }
@@ -454,9 +474,22 @@ static dlp_status launch_bn(const CUtensorMap &tx, const CUtensorMap &ty, const 
     if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
     const int grid = int(std::min<long long>(q.num_items, sm_count()));
     Params r = q;
-    constexpr int b_stages = B_REGION_BYTES / (2 * BN * BK * 4);
-    r.resident = q.kblocks <= b_stages && grid % q.n_tiles == 0;
-    pointwise_tf32x3_kernel<BN><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, ty, tr, packed, r, status);
+    constexpr int b_stage_bytes = 2 * BN * BK * 4;
+    r.resident = q.kblocks * b_stage_bytes <= MAX_B_BYTES && grid % q.n_tiles == 0;
+    r.b_bytes = (r.resident ? q.kblocks : T_STAGES) * b_stage_bytes;
+    // the rest of shared memory in 16 KB units: split between the A ring and the epilogue buffers
+    const int avail = (SMEM_LIMIT - SMEM_FIXED - r.b_bytes) / A_STAGE_BYTES;
+    if(avail <= 6) {
+        // full weights region: a residual operand needs the buffers more than A needs depth
+        r.s_stages = q.has_res ? 2 : 4;
+        r.e_bufs = avail - r.s_stages;
+    }
+    else {
+        r.s_stages = std::min(MAX_S_STAGES - 1, avail / 2);
+        r.e_bufs = std::min(MAX_E_BUFS, avail - r.s_stages);
+    }
+    const int smem_bytes = SMEM_FIXED + r.b_bytes + (r.s_stages + r.e_bufs) * A_STAGE_BYTES;
+    pointwise_tf32x3_kernel<BN><<<grid, NUM_THREADS, smem_bytes, stream>>>(tx, ty, tr, packed, r, status);
     DLP_LAUNCH_OK("pointwise_tf32x3_kernel");
     return DLP_OK;
 }

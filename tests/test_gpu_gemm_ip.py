@@ -133,7 +133,7 @@ def test_gemm_bias_activation_leading_dimensions_and_batches():
     a = rng.standard_normal((B, M, K), dtype=np.float32)
     b = rng.standard_normal((B, K, N), dtype=np.float32)
     g = capi.Gemm(False, False, M, N, K)
-    ws = torch.empty(max(g.workspace(), 16), dtype=torch.uint8, device=DEV)
+    ws = torch.empty(max(g.batched_workspace(B), 16), dtype=torch.uint8, device=DEV)
     c = torch.zeros(B, M, N, device=DEV)
     g.batch_gemm(B, M, N, K, to_dev(a), M * K, K, to_dev(b), K * N, N, c, M * N, N, ws=ws)
     want = np.stack([ob.sgemm(a[i], b[i]) for i in range(B)])
