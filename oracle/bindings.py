@@ -218,8 +218,10 @@ def ref():
         R.ref_net_param_name.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_int]
         R.ref_net_param_shape.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int)]
         R.ref_net_tensor_shape.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_int)]
-        for n in ("ref_net_set_param", "ref_net_set_tensor", "ref_net_get_tensor"):
+        for n in ("ref_net_set_param", "ref_net_set_tensor", "ref_net_get_tensor", "ref_net_get_param"):
             getattr(R, n).argtypes = [C.c_void_p, C.c_char_p, _f32p, C.c_ulonglong]
+        for n in ("ref_net_save_params", "ref_net_load_params"):
+            getattr(R, n).argtypes = [C.c_void_p, C.c_char_p]
         R.ref_net_forward.restype = C.c_double
         R.ref_net_forward.argtypes = [C.c_void_p]
         _ref = R
@@ -315,6 +317,22 @@ class RefNet:
         if ref().ref_net_get_tensor(self.h, name.encode(), _ptr(out), out.size) != 0:
             _ref_fail()
         return out
+
+    def get_param(self, name):
+        out = np.empty(self.param_shape(name), dtype=np.float32)
+        if ref().ref_net_get_param(self.h, name.encode(), _ptr(out), out.size) != 0:
+            _ref_fail()
+        return out
+
+    def save_params_file(self, path):
+        """The reference's own Net::save_parameters (its DLPW writer)."""
+        if ref().ref_net_save_params(self.h, str(path).encode()) != 0:
+            _ref_fail()
+
+    def load_params_file(self, path):
+        """The reference's own Net::load_parameters (its DLPW reader)."""
+        if ref().ref_net_load_params(self.h, str(path).encode()) != 0:
+            _ref_fail()
 
     def forward(self):
         t = ref().ref_net_forward(self.h)

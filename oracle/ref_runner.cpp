@@ -179,6 +179,31 @@ int ref_net_get_tensor(void *p, char const *name, float *data, unsigned long lon
     return 0;
     REF_GUARD_END(-1)
 }
+int ref_net_get_param(void *p, char const *name, float *data, unsigned long long count)
+{
+    REF_GUARD_BEGIN
+    dlprim::Tensor &t = static_cast<RefNet *>(p)->net->param(name);
+    if(t.shape().total_size() != count)
+        throw dlprim::ValidationError(std::string("size mismatch for parameter ") + name);
+    memcpy(data, t.host_data(), t.memory_size());
+    return 0;
+    REF_GUARD_END(-1)
+}
+/// Net::save_parameters / Net::load_parameters: the reference's own DLPW writer and reader (src/net.cpp:63-101, :227-305).
+int ref_net_save_params(void *p, char const *path)
+{
+    REF_GUARD_BEGIN
+    static_cast<RefNet *>(p)->net->save_parameters(path);
+    return 0;
+    REF_GUARD_END(-1)
+}
+int ref_net_load_params(void *p, char const *path)
+{
+    REF_GUARD_BEGIN
+    static_cast<RefNet *>(p)->net->load_parameters(std::string(path), false);
+    return 0;
+    REF_GUARD_END(-1)
+}
 /// Net::forward on the CPU context; returns wall-clock seconds or a negative value on error.
 double ref_net_forward(void *p)
 {

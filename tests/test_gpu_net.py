@@ -163,3 +163,98 @@ def test_in_place_sum_with_a_side_reader_of_the_shortcut(side_reader_between):
     for r in got:
         assert rel_err(r["x"], want["x"]) <= REL_TOL
         assert rel_err(r["z"], want["z"]) <= REL_TOL
+
+
+_spec2 = importlib.util.spec_from_file_location("make_reference_graph_golden", os.path.join(ROOT, "tests", "golden", "make_reference_graph_golden.py"))
+ref_graph = importlib.util.module_from_spec(_spec2)
+_spec2.loader.exec_module(ref_graph)
+
+
+@pytest.mark.parametrize("flags", [0, 2], ids=["fused+graph", "unfused+graph"])
+def test_the_reference_shipped_resnet50_description_runs_as_it_is(flags):
+    """docs/nets_for_benchmark/resnet50-b16.js of the reference, unchanged but for the batch in its input
+    specification (Convolution2D -> BatchNorm -> Activation un-fused, named parameters, in-place activations, 158
+    operators), loaded by dlprim::Net; its output against the reference's own Net on its CPU context for the same
+    file and the same parameters (committed), and live when the reference CPU build is present."""
+    import json
+    from dlprimitives_b200 import capi, hostapi
+    from oracle import bindings as ob
+    graph = json.load(open(os.path.join(ROOT, "tests", "golden", "reference_resnet50_b16.json")))
+    assert len(graph["operators"]) == 158 and graph["outputs"] == ["loss"]
+    net = hostapi.Net(graph, flags=flags)
+    params = {name: ref_graph.synthetic_parameter(name, net.param_shape(name)) for name in net.param_names()}
+    assert "conv1.weight" in params and "bn1.running_var" in params and "fc.bias" in params     # the file's own parameter names
+    for name, value in params.items():
+        net.set_param(name, value)
+    net.upload_params()
+    x = ref_graph.synthetic_input(graph["inputs"][0]["shape"])
+    results = run_gpu(net, x, outputs=("loss",), repeats=3)
+    for r in results:
+        assert np.array_equal(r["loss"], results[0]["loss"])
+    want = np.load(os.path.join(ROOT, "tests", "golden", "reference_resnet50_b16.npz"))["loss"]
+    assert rel_err(results[0]["loss"], want) <= REL_TOL
+    assert (results[0]["loss"].argmax(1) == want.argmax(1)).all()
+    if ob.ref_available() and flags == 0:
+        ref = ob.RefNet(graph)
+        assert set(ref.param_names()) == set(params)
+        for name in ref.param_names():
+            ref.set_param(name, params[name])
+        ref.set_tensor("data", x)
+        ref.forward()
+        assert np.array_equal(ref.get_tensor("loss"), want)                # the committed output is the reference's
+    assert capi.device_status() == 0
+
+
+def _small_interchange_net():
+    from dlprimitives_b200 import resnet50
+    c = ref_graph.SMALL_NET
+    return resnet50.make_json(c["batch"], c["height"], c["width"], folded=c["folded"], width_div=c["width_div"], classes=c["classes"])
+
+
+def test_parameter_file_written_by_the_reference_is_read(tmp_path):
+    """DLPW interchange, reference -> here: a file written by the reference's Net::save_parameters (src/net.cpp:63-101,
+    committed) loaded by Net::load_parameters here gives bit for bit the results of setting the same values directly."""
+    from dlprimitives_b200 import hostapi
+    graph = _small_interchange_net()
+    a = hostapi.Net(graph)
+    params = {name: ref_graph.synthetic_parameter(name, a.param_shape(name)) for name in a.param_names()}
+    for name, value in params.items():
+        a.set_param(name, value)
+    a.upload_params()
+    b = hostapi.Net(graph)
+    b.load_params_file(os.path.join(ROOT, "tests", "golden", "reference_written.dlp"))
+    x = ref_graph.synthetic_input(graph["inputs"][0]["shape"], seed=5)
+    ya, yb = run_gpu(a, x, repeats=1)[0], run_gpu(b, x, repeats=1)[0]
+    assert np.array_equal(ya["fc"], yb["fc"]) and np.abs(ya["fc"]).max() > 0
+
+
+def test_parameter_file_interchange_with_the_live_reference(tmp_path):
+    """DLPW interchange both ways against the reference's own reader and writer (src/net.cpp:63-101, :227-305): the
+    reference reads the file written here and finds every value bit for bit; the file it writes from those values is
+    read back here with identical results."""
+    from oracle import bindings as ob
+    if not ob.ref_available():
+        pytest.skip("reference CPU build (oracle/_ref) not present")
+    from dlprimitives_b200 import hostapi
+    graph = _small_interchange_net()
+    ours = hostapi.Net(graph)
+    params = {name: ref_graph.synthetic_parameter(name + "#2", ours.param_shape(name)) for name in ours.param_names()}
+    for name, value in params.items():
+        ours.set_param(name, value)
+    ours.upload_params()
+    ours_path, ref_path = str(tmp_path / "ours.dlp"), str(tmp_path / "reference.dlp")
+    ours.save_params_file(ours_path)
+    ref = ob.RefNet(graph)
+    ref.load_params_file(ours_path)
+    assert set(ref.param_names()) == set(params)
+    for name in ref.param_names():
+        assert np.array_equal(ref.get_param(name), params[name]), name
+    ref.save_params_file(ref_path)
+    back = hostapi.Net(graph)
+    back.load_params_file(ref_path)
+    x = ref_graph.synthetic_input(graph["inputs"][0]["shape"], seed=6)
+    assert np.array_equal(run_gpu(ours, x, repeats=1)[0]["fc"], run_gpu(back, x, repeats=1)[0]["fc"])
+    # and the reference computes the same network from the file written here
+    ref.set_tensor("data", x)
+    ref.forward()
+    assert rel_err(run_gpu(ours, x, repeats=1)[0]["fc"], ref.get_tensor("fc")) <= REL_TOL
