@@ -126,7 +126,9 @@ int dlp_net_create(const char *net_json, int device, int flags, dlp_net **out)
     h->net.keep_intermediate_tensors((flags & 1) != 0);
     h->net.fuse_operators((flags & 2) == 0);
     h->net.use_cuda_graph((flags & 4) == 0);
-    h->net.load_from_json(json::parse(net_json));
+    json::value description = json::parse(net_json);
+    if(flags & 8) Net::merge_activations(description);
+    h->net.load_from_json(description);
     h->net.setup();
     h->plan = h->net.describe_plan();
     *out = h.release();
@@ -282,6 +284,18 @@ int dlp_net_step_description(const dlp_net *net, int index, char *buf, int n)
 size_t dlp_net_activation_bytes(const dlp_net *net, int without_reuse)
 {
     return without_reuse ? net->net.activation_memory_without_reuse() : net->net.activation_memory();
+}
+
+int dlp_host_merge_activations(const char *net_json, char *out, size_t capacity)
+{
+    GUARD_BEGIN
+    json::value v = json::parse(net_json);
+    int merged = Net::merge_activations(v);
+    std::string text = v.save(json::compact);
+    if(text.size() + 1 > capacity) throw ValidationError("output buffer too small for the merged description");
+    memcpy(out, text.c_str(), text.size() + 1);
+    return merged;
+    GUARD_END(-1)
 }
 
 int dlp_host_gemm(int device, int trans_a, int trans_b, int plan_m, int plan_n, int plan_k, int M, int N, int K, int bias_mode, int activation,

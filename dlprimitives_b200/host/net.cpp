@@ -52,6 +52,40 @@ void Net::load_from_json(json::value const &v)
     }
 }
 
+int Net::merge_activations(json::value &network)
+{
+    json::array &src = network["operators"].array();
+    // every consumer of a tensor name, over the whole description, and the network's outputs
+    std::map<std::string, int> uses;
+    for(json::value const &op : src)
+        for(std::string const &in : op.get("inputs", std::vector<std::string>())) uses[in]++;
+    std::set<std::string> net_outputs;
+    for(json::value const &o : network["outputs"].array()) net_outputs.insert(o.type() == json::is_string ? o.str() : o.get<std::string>("name"));
+    json::array kept;
+    int merged = 0;
+    for(json::value const &op : src) {
+        bool merge = false;
+        if(op.get<std::string>("type") == "Activation" && !kept.empty()) {
+            json::value &prev = kept.back();                      // "directly follows": the operator kept last
+            std::string type = prev.get<std::string>("type");
+            std::vector<std::string> prev_out = prev.get("outputs", std::vector<std::string>());
+            std::vector<std::string> in = op.get("inputs", std::vector<std::string>());
+            std::vector<std::string> out = op.get("outputs", std::vector<std::string>());
+            merge = (type == "Convolution2D" || type == "InnerProduct" || type == "Elementwise") && in.size() == 1 && out.size() == 1
+                    && prev_out.size() == 1 && prev_out[0] == in[0] && prev.get("options.activation", "identity") == "identity"
+                    && uses[in[0]] == 1 && !net_outputs.count(in[0]);
+            if(merge) {
+                prev["outputs"].array()[0] = json::value(out[0]);
+                prev["options"]["activation"] = json::value(op.get("options.activation", "identity"));
+                merged++;
+            }
+        }
+        if(!merge) kept.push_back(op);
+    }
+    src = kept;
+    return merged;
+}
+
 void Net::load_from_json_file(std::string const &name)
 {
     std::ifstream f(name);

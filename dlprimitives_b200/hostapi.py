@@ -46,6 +46,7 @@ SYMBOLS = {
     "dlp_net_num_steps": (_i, [_vp]),
     "dlp_net_step_description": (_i, [_vp, _i, C.c_char_p, _i]),
     "dlp_net_activation_bytes": (_sz, [_vp, _i]),
+    "dlp_host_merge_activations": (_i, [C.c_char_p, C.c_char_p, _sz]),
     "dlp_host_gemm": (_i, [_i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp, _i, _vp, C.c_float, _vp]),
     "dlp_host_batch_sgemm": (_i, [_i, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _i, _i, C.c_float, _vp]),
     "dlp_host_conv_gemm": (_i, [_i, _ip, _i, _i, _i, _i, _vp, _vp, _vp, _vp, C.c_float, _vp]),
@@ -291,3 +292,14 @@ def conv_gemm(x, w, bias, y, stride=1, pad=0, dilate=1, groups=1, activation="id
     if lib().dlp_host_conv_gemm(device, arr, cout // groups, n, int(bias is not None), capi._act(activation), _dptr(w), _dptr(x), _dptr(y),
                                 _dptr(bias), float(factor), _stream(stream)):
         _fail()
+
+
+def merge_activations(net_json):
+    """Net::merge_activations on a network description (dict or JSON text); returns (merged description as a dict, count).
+    Needs no device."""
+    text = net_json if isinstance(net_json, str) else json.dumps(net_json)
+    buf = C.create_string_buffer(len(text) + 1024)
+    n = lib().dlp_host_merge_activations(text.encode(), buf, len(buf))
+    if n < 0:
+        _fail()
+    return json.loads(buf.value.decode()), n

@@ -42,7 +42,8 @@ DLP_HOST_API int dlp_op_forward(dlp_op *op, void *const *device_inputs, void *co
 
 /* ---- a whole network (include/dlprim/net.hpp) ---- */
 typedef struct dlp_net dlp_net;
-/* flags: bit 0 keep intermediate tensors, bit 1 no operator fusion, bit 2 no CUDA graph */
+/* flags: bit 0 keep intermediate tensors, bit 1 no operator fusion, bit 2 no CUDA graph, bit 3 run Net::merge_activations on
+ * the description first */
 DLP_HOST_API int dlp_net_create(const char *net_json, int device, int flags, dlp_net **out);
 DLP_HOST_API void dlp_net_destroy(dlp_net *net);
 DLP_HOST_API int dlp_net_num_params(const dlp_net *net);
@@ -71,6 +72,10 @@ DLP_HOST_API int dlp_net_copy_tensor_from_device(dlp_net *net, const char *name,
 DLP_HOST_API int dlp_net_num_steps(const dlp_net *net);
 DLP_HOST_API int dlp_net_step_description(const dlp_net *net, int index, char *buf, int buf_size);
 DLP_HOST_API size_t dlp_net_activation_bytes(const dlp_net *net, int without_reuse);
+
+/* Net::merge_activations on a network description given as JSON text (no device involved): writes the resulting description
+ * into out (capacity bytes, NUL-terminated) and returns the number of Activation operators merged, or -1 on failure. */
+DLP_HOST_API int dlp_host_merge_activations(const char *net_json, char *out, size_t capacity);
 
 /* ---- gpu::GEMM (include/dlprim/gpu/gemm.hpp), on device buffers; each call makes the object, runs it and lets it go ---- */
 /* GEMM::get_optimal_gemm(...)->gemm(...): C[M,N] = beta*C + act(op(A)*op(B) + bias); the object is made for (plan_m, plan_n,

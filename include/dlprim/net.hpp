@@ -26,6 +26,13 @@ public:
     Net(Net const &) = delete;
     Net const &operator=(Net const &) = delete;
 
+        /// The activation merge of the reference's ONNX importer (src/importers/onnx.cpp:531-579), as a pass over a
+        /// network description that is already JSON: an Activation operator that directly follows a Convolution2D,
+        /// InnerProduct or Elementwise operator whose own activation is "identity", consumes that operator's output
+        /// and is its only consumer (the tensor is not a network output either) disappears into the operator's
+        /// "activation" option, and the operator writes the activation's output tensor.  Returns the number merged.
+        static int merge_activations(json::value &network);
+
     void load_from_json(json::value const &v);
     void load_from_json_file(std::string const &name);
     void add_input_tensor(std::string const &name, TensorSpecs const &ts, bool requires_gradient = false);

@@ -258,3 +258,23 @@ def test_parameter_file_interchange_with_the_live_reference(tmp_path):
     ref.set_tensor("data", x)
     ref.forward()
     assert rel_err(run_gpu(ours, x, repeats=1)[0]["fc"], ref.get_tensor("fc")) <= REL_TOL
+
+
+def test_activation_merge_keeps_the_results():
+    """The description with its mergeable activations merged (flag bit 3) computes bit for bit what the unmerged one does."""
+    from dlprimitives_b200 import hostapi, resnet50
+    from test_host_logic import merge_cases_graph
+    graph = merge_cases_graph()
+    rng = np.random.default_rng(31)
+    plain, merged = hostapi.Net(graph), hostapi.Net(graph, flags=8)
+    assert len(merged.plan()) == len(plain.plan()) - 3
+    for net in (plain, merged):
+        r = np.random.default_rng(32)
+        for name in sorted(net.param_names()):
+            shape = net.param_shape(name)
+            net.set_param(name, (r.standard_normal(shape) * 0.5).astype(np.float32))
+        net.upload_params()
+    x = rng.standard_normal((2, 8, 6, 6), dtype=np.float32)
+    a = run_gpu(plain, x, outputs=("t11", "t15"), repeats=2)[-1]
+    b = run_gpu(merged, x, outputs=("t11", "t15"), repeats=2)[-1]
+    assert np.array_equal(a["t11"], b["t11"]) and np.array_equal(a["t15"], b["t15"])
