@@ -55,6 +55,7 @@ SYMBOLS = {
     "dlp_version": (C.c_char_p, []),
     "dlp_launch_count": (C.c_uint64, []),
     "dlp_device_status": (_i, [_vp, _ip]),
+    "dlp_selftest_wait_expiry": (_i, [C.POINTER(C.c_int * 4), _vp]),
     "dlp_conv2d_output_shape": (_i, [C.POINTER(ConvDesc), _i, _i, _ip, _ip]),
     "dlp_conv2d_fwd_create": (_i, [C.POINTER(ConvDesc), C.POINTER(_vp)]),
     "dlp_conv2d_fwd_destroy": (None, [_vp]),
@@ -157,6 +158,16 @@ def device_status(stream=None):
     if st not in (OK, TIMEOUT):
         check(st)
     return code.value
+
+
+SELFTEST_WAIT_CODE = 900
+
+
+def selftest_wait_expiry(stream=None):
+    """Run the bounded-wait self-test kernel; returns (warp 0 succeeded, its wait in ms, warp 1 succeeded, its wait in ms)."""
+    observed = (C.c_int * 4)()
+    check(lib().dlp_selftest_wait_expiry(C.byref(observed), _stream(stream)))
+    return tuple(observed)
 
 
 def make_conv_desc(channels_in, channels_out, kernel, stride=1, dilate=1, pad=0, groups=1, batch=1, height=1, width=1,

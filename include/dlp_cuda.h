@@ -59,6 +59,13 @@ DLP_API uint64_t dlp_launch_count(void);
  * records a code in a per-device word, drains its copies, frees its tensor memory and returns.
  * This call synchronises `stream`, then reads and clears that word: 0 means no wait ever gave up. */
 DLP_API dlp_status dlp_device_status(void *stream, int *code);
+/* Self-test of the bounded waits (no counterpart in the reference; its OpenCL kernels have no device-side waits).  Launches a
+ * one-CTA kernel whose first warp waits on a barrier nothing arrives at, so that it runs into the time limit (0.4 s), and whose
+ * second warp waits on another such barrier and is released by the abort flag the first one raises.  Synchronises the stream.
+ * observed[] = { warp 0's wait succeeded (0 expected), milliseconds it waited, the same two for warp 1 }.  Afterwards
+ * dlp_device_status() returns DLP_TIMEOUT with code DLP_SELFTEST_WAIT_CODE, and the device is as usable as before. */
+#define DLP_SELFTEST_WAIT_CODE 900
+DLP_API dlp_status dlp_selftest_wait_expiry(int observed[4], void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Convolution forward.

@@ -366,3 +366,30 @@ def test_grouped_convolution_on_the_tensor_core_path(cin, cout, groups, k, hw):
     plan.enqueue_packed(xd, plan.prepack(wd), bd, y2, residual=to_dev(res), post_activation="relu")
     assert rel_err(y2.cpu().numpy(), np.maximum(want + res, 0.0)) <= REL_TOL
     assert capi.device_status() == 0
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_device_usable():
+    """Failure detection without a fault: a kernel whose wait can never be satisfied runs into the time limit of the
+    library's bounded waits, the status word reports it as DLP_TIMEOUT with the waiter's code, the role that was only
+    waiting for the first is released by the abort flag, and the next real convolution is computed as usual."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    assert capi.device_status() == 0
+    first_ok, first_ms, second_ok, second_ms = capi.selftest_wait_expiry()
+    assert first_ok == 0 and 300 <= first_ms <= 2000, (first_ok, first_ms)            # gave up at the 0.4 s limit
+    assert second_ok == 0 and second_ms <= first_ms + 50, (second_ok, second_ms)      # released by the abort flag, not by a second limit
+    import ctypes
+    code = ctypes.c_int(0)
+    st = capi.lib().dlp_device_status(None, ctypes.byref(code))
+    assert st == capi.TIMEOUT and code.value == capi.SELFTEST_WAIT_CODE
+    assert "gave up" in capi.lib().dlp_last_error().decode()
+    assert capi.device_status() == 0                                                   # reading the word cleared it
+    rng = np.random.default_rng(44)
+    x = rng.standard_normal((2, 32, 14, 14), dtype=np.float32)
+    w = kaiming(rng, (48, 32, 3, 3))
+    plan = capi.Conv2DForward(channels_in=32, channels_out=48, kernel=3, pad=1, batch=2, height=14, width=14, bias=False, activation="relu")
+    y = torch.empty(plan.output_shape(2), device=DEV)
+    ws = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=DEV)
+    plan.enqueue(to_dev(x), to_dev(w), None, y, ws)
+    assert rel_err(y.cpu().numpy(), ob.conv2d(x, w, None, pad=1, activation="relu")) <= REL_TOL
+    assert capi.device_status() == 0
