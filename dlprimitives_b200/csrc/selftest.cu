@@ -5,7 +5,8 @@
 // leaves its loop, and the kernel ends normally, so the context stays usable and dlp_device_status() reports
 // DLP_TIMEOUT.  This file lets that path be exercised without disturbing a real kernel: a one-CTA kernel whose
 // first warp waits on a barrier that nothing ever arrives at (it runs into the limit), and whose second warp
-// waits on another such barrier and must be released by the abort flag rather than by its own limit.
+// starts waiting on another such barrier half a limit later and must be released by the abort flag rather than
+// by its own limit.
 #include "tc_device.cuh"
 
 namespace dlp {
@@ -23,6 +24,11 @@ __global__ void __launch_bounds__(64, 1) wait_expiry_kernel(int *status, int *ob
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // warp 1 starts its wait half a limit later than warp 0, so that its own limit cannot be the one that ends it
+    if(warp == 1) {
+        const long long start = tc::global_ns();
+        while(tc::global_ns() - start < tc::WAIT_LIMIT_NS / 2) __nanosleep(1000);
+    }
     const long long t0 = tc::global_ns();
     // warp 0 runs into the time limit; warp 1 is let go by the abort flag warp 0 raises
     const bool ok = tc::warp_wait(&never[warp], 0, &abort_flag, status, DLP_SELFTEST_WAIT_CODE + warp, lane);

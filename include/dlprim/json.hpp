@@ -69,10 +69,18 @@ namespace json {
 
         template<typename T> T get_value() const;
         template<typename T> T get(std::string const &path) const { return at(path).get_value<T>(); }
+        /// The default also stands in when the member exists but cannot be converted to T, as in the reference
+        /// (include/dlprim/json.hpp:918-950): its own network files write booleans as 0 / 1 in places.
         template<typename T> T get(std::string const &path, T const &def) const
         {
             value const &v = find(path);
-            return v.is_undefined() ? def : v.get_value<T>();
+            if(v.is_undefined()) return def;
+            try {
+                return v.get_value<T>();
+            }
+            catch(bad_value_cast const &) {
+                return def;
+            }
         }
         std::string get(std::string const &path, char const *def) const { return get<std::string>(path, std::string(def)); }
 

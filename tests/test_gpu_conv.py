@@ -377,7 +377,7 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_device_usable()
     assert capi.device_status() == 0
     first_ok, first_ms, second_ok, second_ms = capi.selftest_wait_expiry()
     assert first_ok == 0 and 300 <= first_ms <= 2000, (first_ok, first_ms)            # gave up at the 0.4 s limit
-    assert second_ok == 0 and second_ms <= first_ms + 50, (second_ok, second_ms)      # released by the abort flag, not by a second limit
+    assert second_ok == 0 and second_ms <= first_ms - 100, (second_ok, second_ms)     # it began later and was released by the abort flag
     import ctypes
     code = ctypes.c_int(0)
     st = capi.lib().dlp_device_status(None, ctypes.byref(code))
