@@ -40,6 +40,19 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def committed_traffic():
+    """DRAM bytes per contraction launch from the committed profiler summary, or None when it has no such line."""
+    path = os.path.join(ROOT, "profiles", "contraction_tf32x3_forward_dram_traffic.md")
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.startswith("traffic_bytes_per_launch_batch256:"):
+                    return float(line.split(":", 1)[1])
+    except OSError:
+        pass
+    return None
+
+
 def shard(total, world, rank):
     """Images [begin, end) of the global batch that belong to `rank`."""
     base, extra = divmod(total, world)
@@ -245,6 +258,7 @@ def layer_table(net_json, plan, step_ms, batch, peaks):
         info[op["name"]] = {"flops": flops, "bytes": in_bytes + 4 * int(np.prod(out)) + wbytes, "out": out}
     rows = []
     tensor_peak = peaks["bf16_tflops_sustained"] / 2.0 / 3.0      # TF32 = bf16/2, three products per term
+    ridge = tensor_peak * 1e3 / peaks["hbm_gbs"]                  # FLOP per byte above which the tensor roof is the lower one
     for line, ms in zip(plan, step_ms):
         name = line.split(" ")[0]
         i = dict(info[name])
@@ -254,10 +268,12 @@ def layer_table(net_json, plan, step_ms, batch, peaks):
             i["bytes"] += 4 * int(np.prod(i["out"]))             # the residual operand is read as well
         tflops = i["flops"] / ms / 1e9 if ms > 0 else 0.0
         gbs = i["bytes"] / ms / 1e6 if ms > 0 else 0.0
-        tensor_bound = "tf32x3" in line
+        # the applicable roof: the lower of the two for this step's arithmetic intensity
+        intensity = i["flops"] / i["bytes"] if i["bytes"] else 0.0
+        tensor_bound = "tf32x3" in line and intensity > ridge
         rows.append({"step": name, "type": ops[name]["type"], "kernel": " ".join(line.split(" ")[2:4]), "fused": fused, "ms": ms,
-                     "gflop": i["flops"] / 1e9, "mbytes": i["bytes"] / 1e6, "tflops": tflops, "gbs": gbs,
-                     "bound": "tensor" if tensor_bound else "hbm",
+                     "gflop": i["flops"] / 1e9, "mbytes": i["bytes"] / 1e6, "tflops": tflops, "gbs": gbs, "flop_per_byte": intensity,
+                     "tensor_core": "tf32x3" in line, "bound": "tensor" if tensor_bound else "hbm",
                      "frac": (tflops / tensor_peak) if tensor_bound else (gbs / peaks["hbm_gbs"])})
     return rows, tensor_peak
 
@@ -396,17 +412,28 @@ def run_gpu_arm(args, rank, world, local_rank):
     value = GLOBAL_BATCH / (ms_per_step / 1000.0)
     e2e_value = GLOBAL_BATCH / (ms_e2e / args.steps / 1000.0)
     rows, tensor_peak = layer_table(net_json, plan, step_ms, local_batch, peaks)
-    tc = [r for r in rows if r["bound"] == "tensor"]
+    tc = [r for r in rows if r["tensor_core"]]
     tc_ms, tc_flops = sum(r["ms"] for r in tc), sum(r["gflop"] for r in tc)
     achieved = tc_flops / tc_ms if tc_ms > 0 else 0.0      # GFLOP / ms = TFLOP/s
-    # DRAM bytes per contraction launch, from one ncu pass over a forward at 256 images on one GPU
-    # (profiles/contraction_tf32x3_forward_dram_traffic.md); not measured for other per-GPU batches
-    traffic = 486.0e6 if local_batch == 256 else None
-    roofline = {"bound": "tensor", "kernel": "contraction_tf32x3_kernel", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
-                "frac": achieved / tensor_peak, "traffic": traffic, "traffic_unit": "DRAM bytes per launch, average over the forward's launches",
+    # Every launch against its own applicable roof (tensor or HBM, by arithmetic intensity): the time the roofs allow over the time taken.
+    roof_ms = sum(max(r["gflop"] / tensor_peak, r["mbytes"] / peaks["hbm_gbs"]) for r in tc)
+    # DRAM bytes per contraction launch come from a committed profiler summary (a line "traffic_bytes_per_launch_batch256: N");
+    # measured at 256 images on one GPU only
+    traffic = committed_traffic() if local_batch == 256 else None
+    with torch.cuda.stream(stream):
+        tf32_rate = capi.tf32_mma_rate(stream)              # the tensor pipe's own dense TF32 rate on this GPU, now
+    roofline = {"bound": "tensor", "kernel": "contraction_tf32x3_kernel + pointwise_tf32x3_kernel", "achieved": achieved, "peak": tensor_peak,
+                "unit": "TFLOP/s", "frac": achieved / tensor_peak, "traffic": traffic,
+                "traffic_unit": "DRAM bytes per launch, average over the forward's launches",
                 "algorithmic_bytes_per_launch": 1e6 * sum(r["mbytes"] for r in tc) / max(len(tc), 1), "launches": len(tc), "avg_launch_ms": tc_ms / max(len(tc), 1),
                 "peak_source": "%s bf16 sustained %.1f TFLOP/s / 2 (TF32) / 3 (products per term)" % (peaks["source"], peaks["bf16_tflops_sustained"]),
-                "share_of_forward": tc_ms / sum(r["ms"] for r in rows)}
+                "share_of_forward": tc_ms / sum(r["ms"] for r in rows),
+                "frac_applicable": roof_ms / tc_ms if tc_ms > 0 else 0.0,
+                "frac_applicable_note": "sum over the launches of max(FLOP / tensor peak, bytes / HBM peak) over their measured time",
+                "launches_below_0.6": [r["step"] for r in tc if r["frac"] < 0.6],
+                "tf32_measured": tf32_rate, "tf32x3_measured": tf32_rate / 3.0,
+                "tf32_measured_note": "dense TF32 TFLOP/s of an MMA-only kernel on this GPU in this run; a 3xTF32 kernel can reach a third of it",
+                "frac_of_tf32x3_measured": achieved / (tf32_rate / 3.0) if tf32_rate > 0 else None}
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -415,9 +442,8 @@ def run_gpu_arm(args, rank, world, local_rank):
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         cpu["max_abs_prob_diff_vs_gpu"] = err
 
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
-        with open(os.path.join(out_dir, "bench_layers_n%d.json" % world), "w") as f:
+    if args.layers_out:
+        with open(args.layers_out, "w") as f:
             json.dump({"local_batch": local_batch, "tensor_peak_tflops": tensor_peak, "hbm_peak_gbs": peaks["hbm_gbs"], "rows": rows}, f, indent=1)
 
     line = {"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -481,6 +507,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--conv-algo", default="", help="algorithm request for --conv: '', gemm, winograd, depthwise_separable")
+    ap.add_argument("--layers-out", default=None, help="write the per-layer table (time, FLOP, bytes, applicable roof, fraction) to this JSON file")
     ap.add_argument("--conv", default=None, help="profile one convolution instead: N,Cin,H,Cout,K,stride,pad[,groups[,residual]]")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -56,6 +56,7 @@ SYMBOLS = {
     "dlp_launch_count": (C.c_uint64, []),
     "dlp_device_status": (_i, [_vp, _ip]),
     "dlp_selftest_wait_expiry": (_i, [C.POINTER(C.c_int * 4), _vp]),
+    "dlp_tf32_mma_rate": (_i, [C.POINTER(C.c_double), _vp]),
     "dlp_conv2d_output_shape": (_i, [C.POINTER(ConvDesc), _i, _i, _ip, _ip]),
     "dlp_conv2d_fwd_create": (_i, [C.POINTER(ConvDesc), C.POINTER(_vp)]),
     "dlp_conv2d_fwd_destroy": (None, [_vp]),
@@ -168,6 +169,13 @@ def selftest_wait_expiry(stream=None):
     observed = (C.c_int * 4)()
     check(lib().dlp_selftest_wait_expiry(C.byref(observed), _stream(stream)))
     return tuple(observed)
+
+
+def tf32_mma_rate(stream=None):
+    """Measured dense TF32 rate of the tensor pipe on the current device, TFLOP/s (MMA-only kernel, about 2 ms)."""
+    v = C.c_double(0.0)
+    check(lib().dlp_tf32_mma_rate(C.byref(v), _stream(stream)))
+    return v.value
 
 
 def make_conv_desc(channels_in, channels_out, kernel, stride=1, dilate=1, pad=0, groups=1, batch=1, height=1, width=1,

@@ -1,4 +1,4 @@
-// Self-test of the bounded device-side waits.
+// Self-tests and probes: the bounded device-side waits, and the tensor pipe's own TF32 rate.
 //
 // Every mbarrier wait of the tensor-core kernels gives up after a time limit: the waiting thread raises the CTA's
 // abort flag and leaves a code in the device status word, every other role sees the flag at its next wait and
@@ -39,10 +39,98 @@ __global__ void __launch_bounds__(64, 1) wait_expiry_kernel(int *status, int *ob
     }
 }
 
+// ---- raw tensor-core rate: every CTA's one issuing thread sends `iters` x 16 tcgen05.mma.kind::tf32 (M = 128, N = 128, K = 8,
+// A from tensor memory, B from shared memory: the operand placement of the contraction kernels) over zeroed operands and
+// waits for the last to retire.  Nothing is loaded or stored: the time is the tensor pipe's.
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int iters, int *status)
+{
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ unsigned long long done;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_flag;
+    unsigned char *smem = smem_raw + ((1024u - (tc::smem_u32(smem_raw) & 1023u)) & 1023u);
+    for(int i = threadIdx.x; i < 128 * 32; i += 128) reinterpret_cast<float *>(smem)[i] = 0.0f;      // one B tile: 128 rows x 128 bytes
+    if(threadIdx.x == 0) {
+        tc::mbar_init(&done, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    tc::fence_proxy_async_shared();
+    const int warp = threadIdx.x >> 5;
+    if(warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(&tmem_base_s)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem_base = *(volatile uint32_t *)&tmem_base_s;
+    // zero the A columns this test reads (tensor memory is not cleared on allocation): lanes = rows, 32 columns from 256
+    {
+        uint32_t z[16];
+        #pragma unroll
+        for(int i = 0; i < 16; i++) z[i] = 0u;
+        const uint32_t t = tmem_base + (uint32_t(warp * 32) << 16) + 256;
+        tc::tmem_st16(t, z);
+        tc::tmem_st16(t + 16, z);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    if(threadIdx.x == 0) {
+        constexpr uint32_t idesc = tc::instr_desc_tf32(128);
+        constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+        const uint64_t bdesc = (uint64_t(DESC_HI) << 32) | (((tc::smem_u32(smem) & 0x3FFFF) >> 4) | (1u << 16));
+        const uint32_t d = tmem_base, a = tmem_base + 256;
+        for(int i = 0; i < iters; i++) {
+            #pragma unroll
+            for(int j = 0; j < 16; j++)
+                asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+                             ::"r"(d), "r"(a + (j & 3) * 8), "l"(bdesc + 2 * (j & 3)), "r"(idesc), "r"(1) : "memory");
+        }
+        tc::mma_commit(tc::smem_u32(&done));
+        tc::mbar_wait(&done, 0, &abort_flag, status, DLP_SELFTEST_WAIT_CODE + 10);
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    if(warp == 0) {
+        tc::tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
 } // namespace
 } // namespace dlp
 
 using namespace dlp;
+
+extern "C" dlp_status dlp_tf32_mma_rate(double *tflops, void *stream)
+{
+    DLP_REQUIRE(tflops != nullptr, "null result pointer");
+    int *status = device_status_word();
+    if(!status) return fail(DLP_CUDA_ERROR, "cannot resolve the device status word");
+    const int smem = 1024 + 128 * 128;
+    const int ctas = sm_count(), iters = 4000;            // 64 000 MMAs of 64 cycles each per SM: about 2 ms
+    cudaEvent_t e0, e1;
+    DLP_CUDA_OK(cudaEventCreate(&e0));
+    DLP_CUDA_OK(cudaEventCreate(&e1));
+    cudaStream_t s = (cudaStream_t)stream;
+    mma_rate_kernel<<<ctas, 128, smem, s>>>(200, status);                        // warm-up
+    cudaError_t e = cudaEventRecord(e0, s);
+    mma_rate_kernel<<<ctas, 128, smem, s>>>(iters, status);
+    count_launch(2);
+    if(e == cudaSuccess) e = cudaEventRecord(e1, s);
+    if(e == cudaSuccess) e = cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    if(e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if(e == cudaSuccess) e = cudaPeekAtLastError();
+    DLP_CUDA_OK(e);
+    *tflops = ms > 0.0f ? double(ctas) * iters * 16 * (2.0 * 128 * 128 * 8) / (ms * 1e9) : 0.0;
+    return DLP_OK;
+}
 
 extern "C" dlp_status dlp_selftest_wait_expiry(int observed[4], void *stream)
 {

@@ -6,7 +6,7 @@ layer shapes at batch 64, the same work and byte counts (flops = 2 * |Y| * Cin/g
 bytes = 4 * (|X| + |Y| + |W|)), timed with CUDA events over repeated launches after a warm-up, reported
 against the measured tensor-core and HBM peaks.  Forward only.
 
-    python -m dlprimitives_b200.flops [--batch 64] [--csv report.csv] [--gemm] [--algo winograd]
+    python -m dlprimitives_b200.flops [--batch 64] [--full] [--csv report.csv] [--gemm] [--algo winograd]
 """
 import argparse
 import json
@@ -41,13 +41,37 @@ CONV_SHAPES = [
     (1, 0, 1, 256, 256, 256, 56, "scale"),
     (1, 0, 1, 1024, 1024, 1024, 7, "scale"),
 ]
+# The further layer shapes the reference tool adds when it is built with FULL_TEST (tools/flops.cpp:709-760), which then
+# also runs batches 16, 64 and 128: --full here.
+FULL_CONV_SHAPES = [
+    (3, 1, 1, 1, 192, 384, 13, "alexnet"), (3, 1, 1, 1, 256, 256, 13, "alexnet"), (3, 1, 1, 2, 384, 256, 13, "alexnet"),
+    (11, 2, 4, 1, 3, 96, 224, "alexnet"),
+    (1, 0, 1, 1, 1024, 512, 14, "resnet"), (3, 1, 1, 1, 128, 128, 28, "resnet"), (3, 1, 2, 1, 128, 128, 56, "resnet"),
+    (1, 0, 1, 1, 128, 512, 28, "resnet"), (1, 0, 1, 1, 2048, 512, 7, "resnet"), (1, 0, 1, 1, 256, 1024, 14, "resnet"),
+    (1, 0, 1, 1, 256, 128, 56, "resnet"), (3, 1, 2, 1, 256, 256, 28, "resnet"), (1, 0, 2, 1, 256, 512, 56, "resnet"),
+    (1, 0, 1, 1, 256, 64, 56, "resnet"), (1, 0, 2, 1, 512, 1024, 28, "resnet"), (1, 0, 1, 1, 512, 128, 28, "resnet"),
+    (1, 0, 1, 1, 512, 2048, 7, "resnet"), (1, 0, 1, 1, 512, 256, 28, "resnet"), (3, 1, 1, 1, 512, 512, 7, "resnet"),
+    (3, 1, 2, 1, 512, 512, 14, "resnet"),
+    (3, 1, 1, 1, 128, 128, 112, "vgg"), (3, 1, 1, 1, 128, 256, 56, "vgg"), (3, 1, 1, 1, 256, 256, 56, "vgg"),
+    (3, 1, 1, 1, 256, 512, 28, "vgg"), (3, 1, 1, 1, 512, 512, 14, "vgg"), (3, 1, 1, 1, 64, 128, 112, "vgg"),
+    (1, 0, 1, 1, 144, 32, 28, "mobile"), (1, 0, 1, 1, 160, 960, 7, "mobile"), (1, 0, 1, 1, 16, 96, 112, "mobile"),
+    (3, 1, 1, 192, 192, 192, 28, "mobile"), (3, 1, 2, 192, 192, 192, 28, "mobile"), (1, 0, 1, 1, 192, 32, 28, "mobile"),
+    (1, 0, 1, 1, 192, 64, 14, "mobile"), (1, 0, 1, 1, 320, 1280, 7, "mobile"), (1, 0, 1, 1, 32, 16, 112, "mobile"),
+    (1, 0, 1, 1, 32, 192, 28, "mobile"), (3, 1, 1, 32, 32, 32, 112, "mobile"), (3, 1, 1, 384, 384, 384, 14, "mobile"),
+    (1, 0, 1, 1, 384, 64, 14, "mobile"), (1, 0, 1, 1, 384, 96, 14, "mobile"), (1, 0, 1, 1, 576, 160, 7, "mobile"),
+    (3, 1, 1, 576, 576, 576, 14, "mobile"), (3, 1, 2, 576, 576, 576, 14, "mobile"), (1, 0, 1, 1, 576, 96, 14, "mobile"),
+    (1, 0, 1, 1, 64, 384, 14, "mobile"), (1, 0, 1, 1, 96, 24, 56, "mobile"), (1, 0, 1, 1, 96, 576, 14, "mobile"),
+    (3, 1, 2, 96, 96, 96, 112, "mobile"),
+]
+FULL_BATCHES = (16, 64, 128)
 # (M, N, K): square and skinny products, and the InnerProduct shapes of the classifier heads
 GEMM_SHAPES = [(512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (64, 1000, 2048), (256, 1000, 2048),
                (64, 4096, 9216), (8192, 256, 1024), (12544, 64, 147)]
 
 
 def peaks():
-    """Measured peaks of this pool when the driver's file is there, else the earlier measurement."""
+    """HBM GB/s and 3xTF32 TFLOP/s roofs: from MEASURED_PEAKS.json at the repository root when that file exists (a copy
+    bandwidth and a bf16 GEMM rate measured on the target GPUs), else from an earlier measurement of the same kind."""
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     path = os.path.join(root, "MEASURED_PEAKS.json")
     hbm, bf16 = 6650.0, 1400.0
@@ -73,7 +97,7 @@ def time_launches(fn, warmup, reps):
     return e0.elapsed_time(e1) / reps
 
 
-def run_conv(batch, algo, reps, rows):
+def run_conv(batch, algo, reps, rows, shapes=None):
     import torch
     from . import capi
     hbm, tensor = peaks()
@@ -81,7 +105,7 @@ def run_conv(batch, algo, reps, rows):
     g = torch.Generator(device=dev)
     g.manual_seed(3)
     print("%-8s %-30s %9s %7s %8s %7s  %s" % ("net", "convolution", "GFLOP/s", "% roof", "GB/s", "% HBM", "algorithm / kernel"))
-    for k, pad, stride, groups, cin, cout, dim, net in CONV_SHAPES:
+    for k, pad, stride, groups, cin, cout, dim, net in (shapes or CONV_SHAPES):
         plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, stride=stride, pad=pad, groups=groups, batch=batch,
                                   height=dim, width=dim, bias=False, activation="identity", algo=algo)
         x = torch.randn(batch, cin, dim, dim, device=dev, generator=g)
@@ -132,9 +156,15 @@ def main():
     ap.add_argument("--algo", default="", help="convolution algorithm request: '', gemm, winograd, depthwise_separable")
     ap.add_argument("--gemm", action="store_true", help="sweep the GEMM shapes as well")
     ap.add_argument("--csv", default=None, help="also write the table as CSV")
+    ap.add_argument("--full", action="store_true", help="the reference tool's FULL_TEST sweep: 48 more layer shapes, batches 16, 64 and 128")
     args = ap.parse_args()
     rows = []
-    run_conv(args.batch, args.algo, args.reps, rows)
+    if args.full:
+        for batch in FULL_BATCHES:
+            print("batch %d" % batch)
+            run_conv(batch, args.algo, args.reps, rows, CONV_SHAPES + FULL_CONV_SHAPES)
+    else:
+        run_conv(args.batch, args.algo, args.reps, rows)
     if args.gemm:
         run_gemm(args.reps, rows)
     if args.csv:

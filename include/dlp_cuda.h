@@ -66,6 +66,10 @@ DLP_API dlp_status dlp_device_status(void *stream, int *code);
  * dlp_device_status() returns DLP_TIMEOUT with code DLP_SELFTEST_WAIT_CODE, and the device is as usable as before. */
 #define DLP_SELFTEST_WAIT_CODE 900
 DLP_API dlp_status dlp_selftest_wait_expiry(int observed[4], void *stream);
+/* The tensor pipe's own dense TF32 rate on the current device, in TFLOP/s (no counterpart in the reference): every SM issues
+ * tcgen05.mma.kind::tf32 (M 128, N 128, K 8) back to back with nothing loaded or stored, timed with events on the stream
+ * (about 2 ms; synchronises).  The 3xTF32 kernels can reach a third of it.  It is what roofline fractions are put beside. */
+DLP_API dlp_status dlp_tf32_mma_rate(double *tflops, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Convolution forward.
