@@ -262,14 +262,6 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             const uint32_t ns = (s + n) & (STAGES - 1), nphase = ns < s ? s_phase ^ 1 : s_phase;
             const int n_in_chunk = closes_chunk ? 0 : in_chunk + n, nkb = kb + n == kblocks ? 0 : kb + n;
             const uint32_t nchunk = closes_chunk ? chunk + 1 : chunk;
-            bool peek = it + n < total;
-            if(peek) {
-                const bool npair = pairable(ns, n_in_chunk, nkb);
-                const bool mine = lane < 2 || (lane < 4 && npair) || (lane == 4 && n_in_chunk == 0);
-                const uint32_t bar = lane == 4 ? acc_empty0 + 8 * (nchunk & 1) : watch_base + 8 * (ns + (lane >> 1));
-                const uint32_t parity = lane == 4 ? ((nchunk >> 1) & 1) ^ 1 : nphase;
-                if(mine) peek = mbar_test(bar, parity);
-            }
             const uint32_t d = tmem_base + buf * BN, a = tmem_base + A_COL_BASE + s * 64;
             const uint32_t bhi = ring_base + s * (B_STAGE_BYTES >> 4), blo = bhi + (B_TILE_BYTES >> 4);
             uint32_t ah[2][4], al[2][4];
@@ -295,6 +287,17 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 if(pair || (s & 1)) mma_commit(empty0 + 8 * (s >> 1));   // frees the A columns and the B tiles of a pair of stages
                 if(closes_chunk) mma_commit(acc_full0 + 8 * buf);
                 TC_TRACE(3, it);
+            }
+            // A look at the next iteration's barriers now that this one's MMAs are queued: the tensor core needs about as long
+            // for them as the loaders and the B copy need for the next stages, so the answer is usually yes, and a plain
+            // test costs far less than the waits at the top of the loop (a test before the MMAs went out came too early).
+            bool peek = it + n < total;
+            if(peek) {
+                const bool npair = pairable(ns, n_in_chunk, nkb);
+                const bool mine = lane < 2 || (lane < 4 && npair) || (lane == 4 && n_in_chunk == 0);
+                const uint32_t bar = lane == 4 ? acc_empty0 + 8 * (nchunk & 1) : watch_base + 8 * (ns + (lane >> 1));
+                const uint32_t parity = lane == 4 ? ((nchunk >> 1) & 1) ^ 1 : nphase;
+                if(mine) peek = mbar_test(bar, parity);
             }
             ready = __all_sync(0xffffffffu, peek);
             if(lane == 0) TC_TRACE(1, it);
