@@ -174,9 +174,11 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
     else if(algo == "winograd" && square && d.groups == 1 && d.dilate[0] == 1 && d.stride[0] == 1 && d.kernel[0] == 3 && d.pad[0] == 1) {
         // Only on request.  The reference also takes Winograd under "auto" (src/core/conv.cpp:713-720); here
         // the 3xTF32 tensor-core implicit GEMM is the faster kernel for every eligible shape, so "auto" keeps it.
+        // The sixteen products run on the tensor cores unless plain fp32 FMA arithmetic was asked for.
         plan->algo = "winograd";
         plan->kind = CK_WINOGRAD;
-        plan->kernel = "winograd_f23_ffma";
+        plan->winograd_tc = d.math_mode != DLP_MATH_FP32_FFMA;
+        plan->kernel = plan->winograd_tc ? "winograd_f23_tf32x3" : "winograd_f23_ffma";
     }
     else {
         // an incompatible "winograd" or "depthwise_separable" request gets the GEMM algorithm, as in the
@@ -245,12 +247,17 @@ const char *dlp_conv2d_fwd_kernel(const dlp_conv2d_plan *plan) { return plan ? p
 size_t dlp_conv2d_fwd_packed_bytes(const dlp_conv2d_plan *plan)
 {
     if(!plan) return 0;
-    if(plan->kind == CK_WINOGRAD) return winograd_packed_bytes(plan->d.channels_in, plan->d.channels_out);
+    if(plan->kind == CK_WINOGRAD)
+        return plan->winograd_tc ? winograd_tc_packed_bytes(plan->d.channels_in, plan->d.channels_out)
+                                 : winograd_packed_bytes(plan->d.channels_in, plan->d.channels_out);
     return plan->kind == CK_TC ? plan->packed.bytes() * size_t(plan->d.groups) : 0;     // one packed operand per group
 }
 size_t dlp_conv2d_fwd_workspace(const dlp_conv2d_plan *plan)
 {
     const size_t packed = dlp_conv2d_fwd_packed_bytes(plan);
+    if(plan && plan->kind == CK_WINOGRAD && plan->winograd_tc)
+        return align256(packed) + winograd_tc_workspace_bytes(std::max(plan->d.batch, 1), plan->d.channels_in, plan->d.channels_out,
+                                                              plan->d.height, plan->d.width);
     if(!plan || plan->kind != CK_TC) return packed;
     const size_t split = tc_split_scratch_bytes((long long)plan->d.batch * plan->out_h * plan->out_w, plan->packed);
     return split ? align256(packed) + split : packed;
@@ -261,6 +268,8 @@ dlp_status dlp_conv2d_fwd_prepack(const dlp_conv2d_plan *plan, const float *w, v
     DLP_REQUIRE(plan && w, "null argument");
     if(plan->kind == CK_WINOGRAD) {
         DLP_REQUIRE(packed != nullptr, "null packed buffer");
+        if(plan->winograd_tc)
+            return winograd_tc_filter_transform(w, static_cast<float *>(packed), plan->d.channels_in, plan->d.channels_out, (cudaStream_t)stream);
         return winograd_filter_transform(w, static_cast<float *>(packed), plan->d.channels_in, plan->d.channels_out, (cudaStream_t)stream);
     }
     if(plan->kind != CK_TC) return DLP_OK;
@@ -297,6 +306,9 @@ static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, cons
 
     if(plan->kind == CK_WINOGRAD) {
         DLP_REQUIRE(packed != nullptr, "null transformed filters");
+        if(plan->winograd_tc)
+            return launch_winograd_tc(x, packed, bias, y, scratch, scratch_bytes, batch, d.channels_in, d.channels_out, d.height, d.width,
+                                      d.activation, factor, residual, residual_scale, post_act, stream);
         return launch_winograd_f23(x, packed, bias, y, batch, d.channels_in, d.channels_out, d.height, d.width, d.activation, factor,
                                    residual, residual_scale, post_act, stream);
     }

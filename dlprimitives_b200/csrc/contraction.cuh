@@ -161,4 +161,13 @@ dlp_status winograd_filter_transform(const float *w, float *u, int cin, int cout
 dlp_status launch_winograd_f23(const float *x, const float *u, const float *bias, float *y, int batch, int cin, int cout, int h, int w,
                                int act, float factor, const float *residual, float residual_scale, int post_act, cudaStream_t stream);
 
+// Winograd F(2x2, 3x3) with the sixteen products on the tensor cores (winograd_tc.cu): transform, one batched 3xTF32
+// contraction, transform back.  ws: winograd_tc_workspace_bytes() for the batch.
+size_t winograd_tc_packed_bytes(int cin, int cout);
+size_t winograd_tc_workspace_bytes(int batch, int cin, int cout, int h, int w);
+dlp_status winograd_tc_filter_transform(const float *w, float *packed, int cin, int cout, cudaStream_t stream);
+dlp_status launch_winograd_tc(const float *x, const float *packed, const float *bias, float *y, void *ws, size_t ws_bytes, int batch, int cin,
+                              int cout, int h, int w, int act, float factor, const float *residual, float residual_scale, int post_act,
+                              cudaStream_t stream);
+
 } // namespace dlp

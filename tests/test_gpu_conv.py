@@ -212,6 +212,8 @@ def test_algorithm_selection_follows_the_reference_rules():
     assert mk(channels_in=16, channels_out=16, kernel=3, pad=0, algo="winograd").algo() == "gemm"
     assert mk(channels_in=16, channels_out=16, kernel=3, pad=1, stride=2, algo="winograd").algo() == "gemm"
     win = mk(channels_in=16, channels_out=16, kernel=3, pad=1, algo="winograd")
+    assert win.algo() == "winograd" and win.kernel() == "winograd_f23_tf32x3"         # the sixteen products on the tensor cores
+    win = mk(channels_in=16, channels_out=16, kernel=3, pad=1, algo="winograd", math_mode=capi.MATH_FP32_FFMA)
     assert win.algo() == "winograd" and win.kernel() == "winograd_f23_ffma"
     assert win.workspace() >= 16 * 16 * 16 * 4          # the reference's 16*Cin*Cout floats (src/core/conv.cpp:229-232)
     assert mk(channels_in=16, channels_out=16, kernel=3, pad=1).algo() == "gemm"    # "auto" keeps the tensor-core kernel here
@@ -244,8 +246,9 @@ def test_errors_are_reported_not_swallowed():
     plan.enqueue(torch.zeros(0, 8, 8, 8, device=DEV), w, torch.zeros(8, device=DEV), torch.zeros(0, 8, 8, 8, device=DEV), ws)
 
 
+@pytest.mark.parametrize("math_mode", [0, 1], ids=["tensor_cores", "ffma"])
 @pytest.mark.parametrize("cin,hw,cout,batch", [(64, 56, 64, 4), (128, 28, 128, 8), (256, 14, 256, 8), (512, 7, 512, 16), (24, 13, 40, 3)])
-def test_winograd_config_shapes(cin, hw, cout, batch):
+def test_winograd_config_shapes(cin, hw, cout, batch, math_mode):
     """The Winograd benchmark configuration's shapes (and one with odd sizes and ragged channel counts)
     against the CPU checker: plain call with factor, packed call with the fused residual."""
     from dlprimitives_b200 import capi
@@ -256,8 +259,8 @@ def test_winograd_config_shapes(cin, hw, cout, batch):
     w = kaiming(rng, (cout, cin, 3, 3))
     b = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
     plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=3, stride=1, pad=1, batch=batch, height=hw, width=hw,
-                              bias=True, activation="relu", algo="winograd")
-    assert plan.algo() == "winograd"
+                              bias=True, activation="relu", algo="winograd", math_mode=math_mode)
+    assert plan.algo() == "winograd" and plan.kernel() == ("winograd_f23_ffma" if math_mode else "winograd_f23_tf32x3")
     xd, wd, bd = to_dev(x), to_dev(w), to_dev(b)
     want = ob.conv2d(x, w, b, stride=1, pad=1, activation="relu")
     y0 = rng.standard_normal(want.shape, dtype=np.float32)
@@ -268,8 +271,12 @@ def test_winograd_config_shapes(cin, hw, cout, batch):
     res = rng.standard_normal(want.shape, dtype=np.float32)
     packed = plan.prepack(wd)
     y2 = torch.full(plan.output_shape(batch), float("nan"), device=DEV)
-    plan.enqueue_packed(xd, packed, bd, y2, residual=to_dev(res), residual_scale=1.0, post_activation="relu")
+    plan.enqueue_packed(xd, packed, bd, y2, residual=to_dev(res), residual_scale=1.0, post_activation="relu", ws=ws)
     assert rel_err(y2.cpu().numpy(), np.maximum(want + res, 0.0)) <= REL_TOL
+    # a smaller batch than planned runs in the same workspace
+    y3 = torch.empty(plan.output_shape(1), device=DEV)
+    plan.enqueue_packed(xd[:1].contiguous(), packed, bd, y3, ws=ws)
+    assert rel_err(y3.cpu().numpy(), want[:1]) <= REL_TOL
     assert capi.device_status() == 0
 
 
