@@ -483,6 +483,7 @@ def run_single_conv(args):
     res = torch.randn(plan.output_shape(n), device=dev, generator=g) if with_res else None
     extra = dict(residual=res, post_activation="relu") if with_res else {}
     packed = plan.prepack(w)
+    extra["ws"] = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=dev)
     for _ in range(max(args.warmup, 3)):
         plan.enqueue_packed(x, packed, b, y, **extra)
     torch.cuda.synchronize()
