@@ -500,6 +500,103 @@ def run_single_conv(args):
                       "gflop": flops / 1e9, "mbytes": byts / 1e6, "status": capi.device_status()}), flush=True)
 
 
+def run_config_table(args):
+    """The shapes of the benchmark configurations 1-4, one row each: GPU time through the C ABI (packed weights, CUDA events,
+    median of a few bursts), TFLOP/s, GB/s, the applicable roof and the fraction reached, and beside it the reference's own
+    CPU operator (oracle/_ref, one core; the C restatement when that build is absent) timed on one or two images of the row
+    and scaled to its batch.  Prints a markdown table."""
+    import torch
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    peaks = measured_peaks()
+    tensor_peak = peaks["bf16_tflops_sustained"] / 6.0
+    ridge = tensor_peak * 1e3 / peaks["hbm_gbs"]
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    rows = []
+
+    def gpu_time(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / 10)
+        return statistics.median(times)
+
+    def cpu_conv_seconds(x, w, b, opts, images):
+        """Seconds per image of the reference CPU operator (its own code when built here, else the C restatement)."""
+        xs = x[:images].cpu().numpy()
+        if ob.ref_available():
+            op = ob.RefOperator("Convolution2D", opts, [xs.shape])
+            op.forward([xs], [w.cpu().numpy()] + ([b.cpu().numpy()] if b is not None else []))
+            return op.seconds / images, "reference"
+        t0 = time.time()
+        ob.conv2d(xs, w.cpu().numpy(), None if b is None else b.cpu().numpy(), stride=opts["stride"][0], pad=opts["pad"][0], groups=opts["groups"],
+                  activation=opts.get("activation", "identity"))
+        return (time.time() - t0) / images, "port"
+
+    def conv_row(cfg, n, cin, hw, cout, k, stride, pad, groups=1, act="identity", bias=False, algo=""):
+        x = torch.randn(n, cin, hw, hw, device=dev, generator=gen)
+        w = torch.randn(cout, cin // groups, k, k, device=dev, generator=gen) * (2.0 / (cin // groups * k * k)) ** 0.5
+        b = (torch.rand(cout, device=dev, generator=gen) * 0.2 - 0.1) if bias else None
+        plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, stride=stride, pad=pad, groups=groups, batch=n, height=hw,
+                                  width=hw, bias=bias, activation=act, algo=algo)
+        y = torch.empty(plan.output_shape(n), device=dev)
+        ws = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=dev)
+        packed = plan.prepack(w)
+        ms = gpu_time(lambda: plan.enqueue_packed(x, packed, b, y, ws=ws))
+        flops = 2.0 * y.numel() * (cin // groups) * k * k
+        byts = 4.0 * (x.numel() + y.numel() + w.numel() + (cout if bias else 0))
+        opts = {"channels_in": cin, "channels_out": cout, "kernel": [k, k], "stride": [stride, stride], "pad": [pad, pad], "dilate": [1, 1],
+                "groups": groups, "bias": bias, "activation": act}
+        sec, kind = cpu_conv_seconds(x, w, b, opts, 1 if flops / n > 2e8 else 2)
+        rows.append((cfg, "conv %dx%d/%d g%d %d->%d @%d N=%d %s" % (k, k, stride, groups, cin, cout, hw, n, act), plan.algo() + " " + plan.kernel(), ms, flops, byts,
+                     sec * n * 1e3, kind))
+
+    conv_row("1", 16, 64, 56, 64, 3, 1, 1, act="relu", bias=True)
+    # configuration 2: InnerProduct 256 x 2048 -> 1000 and the three 1x1 convolutions
+    x = torch.randn(256, 2048, device=dev, generator=gen)
+    w = torch.randn(1000, 2048, device=dev, generator=gen) * (2.0 / 2048) ** 0.5
+    b = torch.zeros(1000, device=dev)
+    ip = capi.IPForward(2048, 1000, 256, bias=True)
+    y = torch.empty(256, 1000, device=dev)
+    ws = torch.empty(max(ip.workspace(), 16), dtype=torch.uint8, device=dev)
+    packed = ip.prepack(w)
+    ms = gpu_time(lambda: ip.enqueue_packed(x, packed, b, y, ws=ws))
+    t0 = time.time()
+    ob.inner_product(x[:16].cpu().numpy(), w.cpu().numpy(), b.cpu().numpy())
+    rows.append(("2", "InnerProduct 2048->1000 M=256", ip.kernel(), ms, 2.0 * 256 * 1000 * 2048, 4.0 * (x.numel() + y.numel() + w.numel() + 1000),
+                 (time.time() - t0) / 16 * 256 * 1e3, "port"))
+    for cin, cout in ((256, 1024), (1024, 256), (512, 2048)):
+        conv_row("2", 64, cin, 14, cout, 1, 1, 0, bias=True)
+    for c, hw, stride, cout in ((32, 112, 1, 16), (96, 112, 2, 24), (144, 56, 1, 24), (144, 56, 2, 32), (192, 28, 1, 32), (192, 28, 2, 64), (384, 14, 1, 64),
+                                (384, 14, 1, 96), (576, 14, 1, 96), (576, 14, 2, 160), (960, 7, 1, 160), (960, 7, 1, 320)):
+        conv_row("3 dw", 128, c, hw, c, 3, stride, 1, groups=c)
+        conv_row("3 pw", 128, c, (hw + 2 - 3) // stride + 1, cout, 1, 1, 0, act="relu6")
+    for c, hw in ((64, 56), (128, 28), (256, 14), (512, 7)):
+        for algo in ("gemm", "winograd"):
+            conv_row("4 " + algo, 64, c, hw, c, 3, 1, 1, algo=algo)
+    print("| cfg | shape | algorithm / kernel | GPU ms | TFLOP/s | GB/s | FLOP/B | roof | frac | CPU ms (1 core, scaled) | CPU code | GPU/CPU |")
+    print("|---|---|---|---:|---:|---:|---:|---|---:|---:|---|---:|")
+    for cfg, shape, kernel, ms, flops, byts, cpu_ms, kind in rows:
+        tf, gbs, ai = flops / ms / 1e9, byts / ms / 1e6, flops / byts
+        tensor = "tf32x3" in kernel and ai > ridge
+        frac = tf / tensor_peak if tensor else gbs / peaks["hbm_gbs"]
+        print("| %s | %s | %s | %.4f | %.1f | %.0f | %.0f | %s | %.2f | %.0f | %s | %.0fx |"
+              % (cfg, shape, kernel, ms, tf, gbs, ai, "tensor" if tensor else "hbm", frac, cpu_ms, kind, cpu_ms / ms))
+    print()
+    print("roofs: tensor %.1f TFLOP/s (3xTF32 = bf16 sustained / 6), HBM %.1f GB/s (%s); tensor roof applies above %.0f FLOP/B"
+          % (tensor_peak, peaks["hbm_gbs"], peaks["source"], ridge))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -509,6 +606,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--conv-algo", default="", help="algorithm request for --conv: '', gemm, winograd, depthwise_separable")
     ap.add_argument("--layers-out", default=None, help="write the per-layer table (time, FLOP, bytes, applicable roof, fraction) to this JSON file")
+    ap.add_argument("--configs", action="store_true", help="print the per-shape table of benchmark configurations 1-4 (GPU, with the reference CPU time beside it)")
     ap.add_argument("--conv", default=None, help="profile one convolution instead: N,Cin,H,Cout,K,stride,pad[,groups[,residual]]")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -519,6 +617,9 @@ def main():
         return
     if args.conv:
         run_single_conv(args)
+        return
+    if args.configs:
+        run_config_table(args)
         return
     if world != args.gpus:
         raise SystemExit("--gpus %d needs %d ranks (launch with torch.distributed.run --nproc-per-node %d), got WORLD_SIZE=%d"

@@ -48,8 +48,8 @@ constexpr int A_COL_BASE = 256;      // tensor-memory columns [0,256): two parti
 constexpr int TMEM_COLS = 512;
 constexpr int CHUNK_KB = 8;          // k-blocks summed inside the tensor core before the sum moves to fp32 adds
 // Warp roles.  Tensor-memory lanes are tied to (warp index mod 4), so the accumulate and the loader
-// warps start at multiples of four (warp 2 prefetches the residual operand into L2, warp 3 has no role).
-constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_PREFETCH = 2, WARP_ACC0 = 4, WARP_LOAD0 = 8;
+// warps start at multiples of four (warp 2 prefetches the residual operand into L2, warp 3 is the second MMA issuer).
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_PREFETCH = 2, WARP_MMA2 = 3, WARP_ACC0 = 4, WARP_LOAD0 = 8;
 constexpr int NUM_ACC_WARPS = 4, NUM_LOADER_WARPS = 8;
 constexpr int NUM_WARPS = WARP_LOAD0 + NUM_LOADER_WARPS;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
@@ -214,8 +214,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             }
         }
     }
-    else if(warp == WARP_MMA) {
-        // ------------------------------------------------------------------ MMA issuer
+    else if(warp == WARP_MMA || warp == WARP_MMA2) {
+        // ------------------------------------------------------------------ MMA issuers
         // One thread feeds the tensor core, and what it executes per k-block is a dependent scalar chain
         // that has to stay shorter than the tensor core's own time for the k-block.  So:
         //  * the whole warp runs the loop with warp-uniform control flow and every MMA operand is computed
@@ -235,80 +235,86 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         const uint32_t total = uint32_t(my_tiles * kblocks);
         uint32_t chunk = 0, s = 0, s_phase = 0;           // partial accumulators so far; ring position and parity
         int kb = 0, in_chunk = 0;
-        bool ready = false;
         uint32_t it = 0;
         // An iteration takes two k-blocks when they start on an even stage and lie in the same chunk (the usual
         // case): one barrier test, one vote, one release commit and one round of loop bookkeeping for 24 MMAs.
         // Lanes 0,1 watch the first stage, lanes 2,3 the second, lane 4 the read-out of a partial accumulator
         // that the first k-block opens.
         auto pairable = [&](uint32_t st, int ic, int k) { return (st & 1) == 0 && ic + 2 <= CHUNK_KB && k + 2 <= kblocks; };
+        // Two issuer warps take the iterations in turn.  A single issuer is a serial chain -- wait for the stages, build
+        // the operands, issue (which blocks at the tensor core's own pace: its queue is short), commit, vote, loop -- and
+        // everything but the issue leaves the tensor core idle.  With two, warp B waits for its stages and builds its
+        // operands while warp A's MMAs go out, and starts the moment A has issued its last one (a named barrier carries
+        // the turn; tcgen05 fences around it keep the MMAs of the two threads in order), and A's commits and bookkeeping
+        // run under B's MMAs.  Both warps step through the same deterministic sequence of iterations; each acts on every
+        // other one.  A warp whose wait gives up keeps taking its turns without issuing, so the other is never left
+        // alone at the barrier.
+        const int me = warp == WARP_MMA ? 0 : 1;
+        uint32_t step = 0;
+        bool dead = false;
         #pragma unroll 1
         while(it < total) {
             const uint32_t buf = chunk & 1;
             const bool pair = pairable(s, in_chunk, kb);
             const int n = pair ? 2 : 1;
             const bool closes_chunk = in_chunk + n == CHUNK_KB || kb + n == kblocks;
-            if(!ready) {
-                const bool mine = lane < 2 || (lane < 4 && pair) || (lane == 4 && in_chunk == 0);
-                const uint32_t bar = lane == 4 ? acc_empty0 + 8 * buf : watch_base + 8 * (s + (lane >> 1));
-                const uint32_t parity = lane == 4 ? ((chunk >> 1) & 1) ^ 1 : s_phase;
-                const int code = lane == 4 ? ST_MMA_ACC : (lane & 1 ? ST_MMA_FULL_B : ST_MMA_FULL_A);
-                const bool ok = mine ? mbar_wait(bar, parity, &sh->abort_flag, status, code) : true;
-                if(!__all_sync(0xffffffffu, ok)) break;
-            }
-            if(lane == 0) TC_TRACE(2, it);
-            tc_fence_after();
-            // the state of the next iteration, and a look at its barriers
             const uint32_t ns = (s + n) & (STAGES - 1), nphase = ns < s ? s_phase ^ 1 : s_phase;
-            const int n_in_chunk = closes_chunk ? 0 : in_chunk + n, nkb = kb + n == kblocks ? 0 : kb + n;
-            const uint32_t nchunk = closes_chunk ? chunk + 1 : chunk;
-            const uint32_t d = tmem_base + buf * BN, a = tmem_base + A_COL_BASE + s * 64;
-            const uint32_t bhi = ring_base + s * (B_STAGE_BYTES >> 4), blo = bhi + (B_TILE_BYTES >> 4);
-            uint32_t ah[2][4], al[2][4];
-            uint64_t bh[2][4], bl[2][4];
-            #pragma unroll
-            for(int h = 0; h < 2; h++)
+            if(int(step & 1) == me) {
+                if(!dead) {
+                    const bool mine = lane < 2 || (lane < 4 && pair) || (lane == 4 && in_chunk == 0);
+                    const uint32_t bar = lane == 4 ? acc_empty0 + 8 * buf : watch_base + 8 * (s + (lane >> 1));
+                    const uint32_t parity = lane == 4 ? ((chunk >> 1) & 1) ^ 1 : s_phase;
+                    const int code = lane == 4 ? ST_MMA_ACC : (lane & 1 ? ST_MMA_FULL_B : ST_MMA_FULL_A);
+                    const bool ok = mine ? mbar_wait(bar, parity, &sh->abort_flag, status, code) : true;
+                    if(!__all_sync(0xffffffffu, ok)) dead = true;
+                }
+                if(lane == 0 && me == 0) TC_TRACE(2, it);
+                const uint32_t d = tmem_base + buf * BN, a = tmem_base + A_COL_BASE + s * 64;
+                const uint32_t bhi = ring_base + s * (B_STAGE_BYTES >> 4), blo = bhi + (B_TILE_BYTES >> 4);
+                uint32_t ah[2][4], al[2][4];
+                uint64_t bh[2][4], bl[2][4];
                 #pragma unroll
-                for(int j = 0; j < 4; j++) {
-                    // stage h of the pair; K=8 step j: 8 columns further in A, 32 bytes (2 descriptor units) further in the B rows
-                    ah[h][j] = a + h * 64 + 8 * j;
-                    al[h][j] = a + h * 64 + 32 + 8 * j;
-                    bh[h][j] = (uint64_t(DESC_HI) << 32) | (bhi + h * (B_STAGE_BYTES >> 4) + 2 * j);
-                    bl[h][j] = (uint64_t(DESC_HI) << 32) | (blo + h * (B_STAGE_BYTES >> 4) + 2 * j);
+                for(int h = 0; h < 2; h++)
+                    #pragma unroll
+                    for(int j = 0; j < 4; j++) {
+                        // stage h of the pair; K=8 step j: 8 columns further in A, 32 bytes (2 descriptor units) further in the B rows
+                        ah[h][j] = a + h * 64 + 8 * j;
+                        al[h][j] = a + h * 64 + 32 + 8 * j;
+                        bh[h][j] = (uint64_t(DESC_HI) << 32) | (bhi + h * (B_STAGE_BYTES >> 4) + 2 * j);
+                        bl[h][j] = (uint64_t(DESC_HI) << 32) | (blo + h * (B_STAGE_BYTES >> 4) + 2 * j);
+                    }
+                const uint32_t accumulate = in_chunk != 0;
+                // my turn: the other warp has issued the iteration before this one
+                if(step > 0) asm volatile("bar.sync %0, 64;" ::"r"(3 + int((step - 1) & 1)) : "memory");
+                tc_fence_after();
+                if(!dead && elect_one()) {
+                    if(!TC_DIAG(DIAG_NO_MMA)) {
+                        mma_kblock(d, ah[0], al[0], bh[0], bl[0], idesc, accumulate);
+                        if(pair) mma_kblock(d, ah[1], al[1], bh[1], bl[1], idesc, 1u);
+                    }
                 }
-            const uint32_t accumulate = in_chunk != 0;
-            if(elect_one()) {
-                TC_TRACE(6, it);
-                if(!TC_DIAG(DIAG_NO_MMA)) {
-                    mma_kblock(d, ah[0], al[0], bh[0], bl[0], idesc, accumulate);
-                    if(pair) mma_kblock(d, ah[1], al[1], bh[1], bl[1], idesc, 1u);
+                __syncwarp();
+                tc_fence_before();
+                asm volatile("bar.arrive %0, 64;" ::"r"(3 + int(step & 1)) : "memory");      // the other warp's turn
+                if(lane == 0 && me == 0) TC_TRACE(5, it);
+                if(!dead && elect_one()) {
+                    if(pair || (s & 1)) mma_commit(empty0 + 8 * (s >> 1));   // frees the A columns and the B tiles of a pair of stages
+                    if(closes_chunk) mma_commit(acc_full0 + 8 * buf);
                 }
-                TC_TRACE(5, it);
-                if(pair || (s & 1)) mma_commit(empty0 + 8 * (s >> 1));   // frees the A columns and the B tiles of a pair of stages
-                if(closes_chunk) mma_commit(acc_full0 + 8 * buf);
-                TC_TRACE(3, it);
+                __syncwarp();
+                if(lane == 0 && me == 0) TC_TRACE(3, it);
             }
-            // A look at the next iteration's barriers now that this one's MMAs are queued: the tensor core needs about as long
-            // for them as the loaders and the B copy need for the next stages, so the answer is usually yes, and a plain
-            // test costs far less than the waits at the top of the loop (a test before the MMAs went out came too early).
-            bool peek = it + n < total;
-            if(peek) {
-                const bool npair = pairable(ns, n_in_chunk, nkb);
-                const bool mine = lane < 2 || (lane < 4 && npair) || (lane == 4 && n_in_chunk == 0);
-                const uint32_t bar = lane == 4 ? acc_empty0 + 8 * (nchunk & 1) : watch_base + 8 * (ns + (lane >> 1));
-                const uint32_t parity = lane == 4 ? ((nchunk >> 1) & 1) ^ 1 : nphase;
-                if(mine) peek = mbar_test(bar, parity);
-            }
-            ready = __all_sync(0xffffffffu, peek);
-            if(lane == 0) TC_TRACE(1, it);
+            step++;
             it += n;
             s = ns;
             s_phase = nphase;
-            in_chunk = n_in_chunk;
-            kb = nkb;
-            chunk = nchunk;
+            in_chunk = closes_chunk ? 0 : in_chunk + n;
+            kb = kb + n == kblocks ? 0 : kb + n;
+            chunk = closes_chunk ? chunk + 1 : chunk;
         }
-        if(lane == 0) *(volatile uint32_t *)&sh->mma_consumed = it;
+        // the last turn handed over is taken by nobody: meet it so that both barriers are left balanced
+        if(step > 0 && int(step & 1) == me) asm volatile("bar.sync %0, 64;" ::"r"(3 + int((step - 1) & 1)) : "memory");
+        if(lane == 0 && me == 0) *(volatile uint32_t *)&sh->mma_consumed = it;
     }
     else if(warp == WARP_PREFETCH) {
         // ------------------------------------------------------------------ residual prefetcher
@@ -347,7 +353,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         }
     }
     else if(warp < WARP_ACC0) {
-        // warp 3: no role
+        // (no warp left for this branch)
     }
     else if(warp < WARP_LOAD0 || (short_k && warp >= WARP_LOAD0 + 4)) {
         // ------------------------------------------------------------------ accumulate + epilogue
