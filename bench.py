@@ -598,6 +598,7 @@ def run_config_table(args):
 
 
 def main():
+    global GLOBAL_BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -605,10 +606,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--conv-algo", default="", help="algorithm request for --conv: '', gemm, winograd, depthwise_separable")
+    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch; the benchmark configuration is 256 -- other values are for "
+                    "profiler captures on a small case only, and the line then says so in config.global_batch")
     ap.add_argument("--layers-out", default=None, help="write the per-layer table (time, FLOP, bytes, applicable roof, fraction) to this JSON file")
     ap.add_argument("--configs", action="store_true", help="print the per-shape table of benchmark configurations 1-4 (GPU, with the reference CPU time beside it)")
     ap.add_argument("--conv", default=None, help="profile one convolution instead: N,Cin,H,Cout,K,stride,pad[,groups[,residual]]")
     args = ap.parse_args()
+    GLOBAL_BATCH = args.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
