@@ -695,30 +695,52 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
 // Pack B(col, k): zero-padded, split into hi and lo, and laid out as the kernel's shared-memory stages
 // (see TcPacked): stage (column tile, k-block) = hi tile then lo tile, each bn rows of 32 floats with the
 // 16-byte chunks of a row permuted by the 128-byte swizzle (chunk ^ (row & 7)).
+// A thread packs one 16-byte chunk (four consecutive k of one column): the swizzle permutes whole chunks, so the chunk is one
+// 16-byte store per tile.  n_major: consecutive threads take consecutive columns (sources whose columns are contiguous),
+// otherwise consecutive chunks along k (sources whose k is contiguous, read 16 bytes at a time when aligned).
 __global__ void prepack_kernel(const float *__restrict__ b, long long col_stride, long long k_stride, int cols, int k,
-                               int n_pad, int k_pad, int bn, int taps, float *__restrict__ packed, long long b_batch_stride)
+                               int n_pad, int k_pad, int bn, int taps, float *__restrict__ packed, long long b_batch_stride, int n_major)
 {
-    const long long total = (long long)n_pad * k_pad;
+    const int chunks = k_pad / 4;
+    const long long total = (long long)n_pad * chunks;
     b += blockIdx.y * b_batch_stride;           // a batch of matrices: blockIdx.y picks one, packed one after the other
-    packed += blockIdx.y * (2 * total);
+    packed += blockIdx.y * (2ll * n_pad * k_pad);
     const int kblocks = k_pad / BK;
+    const bool vec = !n_major && taps == 0 && k_stride == 1 && (col_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0;
     for(long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
-        const int n = int(idx / k_pad), kk = int(idx - (long long)n * k_pad);
-        const int kb = kk / BK, i = kk % BK;
-        float v = 0.0f;
-        int ks = kk;
-        if(taps > 0) {
-            // packed order (channel block, tap, channel in block) <- source order (channel, tap)
-            const int cb = kb / taps, t = kb % taps;
-            ks = (cb * BK + i) * taps + t;
+        int n, c;
+        if(n_major) { c = int(idx / n_pad); n = int(idx - (long long)c * n_pad); }
+        else { n = int(idx / chunks); c = int(idx - (long long)n * chunks); }
+        const int kk = c * 4, kb = kk / BK, i = kk % BK;
+        float v[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+        if(n < cols) {
+            if(vec && kk + 4 <= k) {
+                const float4 t = __ldg(reinterpret_cast<const float4 *>(b + n * col_stride + kk));
+                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+            }
+            else {
+                #pragma unroll
+                for(int j = 0; j < 4; j++) {
+                    int ks = kk + j;
+                    if(taps > 0) {
+                        // packed order (channel block, tap, channel in block) <- source order (channel, tap)
+                        const int cb = kb / taps, t = kb % taps;
+                        ks = (cb * BK + i + j) * taps + t;
+                    }
+                    if(kk + j < k) v[j] = __ldg(b + n * col_stride + ks * k_stride);
+                }
+            }
         }
-        if(n < cols && kk < k) v = __ldg(b + n * col_stride + ks * k_stride);
-        const float hi = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        float4 hi, lo;
+        hi.x = __uint_as_float(__float_as_uint(v[0]) & 0xffffe000u); lo.x = v[0] - hi.x;
+        hi.y = __uint_as_float(__float_as_uint(v[1]) & 0xffffe000u); lo.y = v[1] - hi.y;
+        hi.z = __uint_as_float(__float_as_uint(v[2]) & 0xffffe000u); lo.z = v[2] - hi.z;
+        hi.w = __uint_as_float(__float_as_uint(v[3]) & 0xffffe000u); lo.w = v[3] - hi.w;
         const int tile = n / bn, r = n % bn;
         const long long stage = ((long long)tile * kblocks + kb) * (2 * bn * BK);
-        const int off = r * BK + (((i >> 2) ^ (r & 7)) << 2) + (i & 3);
-        packed[stage + off] = hi;
-        packed[stage + bn * BK + off] = v - hi;
+        const int off = r * BK + (((i >> 2) ^ (r & 7)) << 2);
+        *reinterpret_cast<float4 *>(packed + stage + off) = hi;
+        *reinterpret_cast<float4 *>(packed + stage + bn * BK + off) = lo;
     }
 }
 
@@ -754,12 +776,12 @@ TcPacked tc_packed_layout(int cols, int k)
 dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
                       float *packed, int taps, cudaStream_t stream, int batch, long long b_batch_stride)
 {
-    const long long total = (long long)L.n_pad * L.k_pad;
+    const long long total = (long long)L.n_pad * (L.k_pad / 4);
     const int threads = 256;
     const int blocks = int(std::min<long long>(ceil_div<long long>(total, threads), 8 * sm_count()));
     if(batch < 1 || batch > 65535) return fail(DLP_INVALID_ARGUMENT, "a batched product takes 1 to 65535 matrices");
     tc::prepack_kernel<<<dim3(blocks, batch), threads, 0, stream>>>(b, b_col_stride, b_k_stride, cols, k, L.n_pad, L.k_pad, L.bn, taps, packed,
-                                                                    b_batch_stride);
+                                                                    b_batch_stride, b_col_stride == 1 && b_k_stride != 1 ? 1 : 0);
     DLP_LAUNCH_OK("prepack_kernel");
     return DLP_OK;
 }
