@@ -197,10 +197,16 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
     plan->strided_a = d.kernel[0] == 1 && d.kernel[1] == 1 && d.stride[0] == 1 && d.stride[1] == 1 && d.pad[0] == 0 && d.pad[1] == 0;
 
     plan->tapblock = plan->kind == CK_TC && !plan->strided_a && (d.channels_in / d.groups) % 32 == 0;
+    // Wide kernels over channel counts that do not come in blocks of 32 (a 7x7 stem over 3 channels): kernel columns padded
+    // to 8 make a k-block four whole kernel rows, which the loaders address row by row instead of element by element.
+    const int row_groups = d.channels_in / d.groups * d.kernel[0];
+    plan->rowtaps = plan->kind == CK_TC && !plan->strided_a && !plan->tapblock && d.dilate[0] == 1 && d.dilate[1] == 1 &&
+                    d.kernel[1] >= 5 && d.kernel[1] <= ROWTAPS_WIDTH && row_groups <= 1024;
     if(plan->kind != CK_DEPTHWISE && plan->kind != CK_WINOGRAD) {
-        plan->packed = tc_packed_layout(d.channels_out / d.groups, plan->k);
+        plan->packed = tc_packed_layout(d.channels_out / d.groups, plan->rowtaps ? row_groups * ROWTAPS_WIDTH : plan->k);
         if(plan->kind == CK_TC)
-            plan->kernel = std::string("igemm_tf32x3_bn") + std::to_string(plan->packed.bn) + (plan->strided_a ? "_1x1" : (plan->tapblock ? "_taps" : "_gather"));
+            plan->kernel = std::string("igemm_tf32x3_bn") + std::to_string(plan->packed.bn) +
+                           (plan->strided_a ? "_1x1" : (plan->tapblock ? "_taps" : (plan->rowtaps ? "_rowtaps" : "_gather")));
         else
             plan->kernel = std::string("igemm_ffma_64x64") + (plan->strided_a ? "_1x1" : "_gather");
         if(!plan->strided_a) {
@@ -220,6 +226,14 @@ dlp_status dlp_conv2d_fwd_create(const dlp_conv2d_desc *desc, dlp_conv2d_plan **
                         taps[ky * d.kernel[1] + kx] = (dy << 16) | dx;
                     }
             for(; idx < k_pad; idx++) { tab[idx].offset = 0; tab[idx].tap = TAP_PADDING; }
+            if(plan->rowtaps) {
+                // one entry per (channel, kernel row); the groups beyond K name a kernel row that never exists
+                for(int g = 0; g < k_pad / ROWTAPS_WIDTH; g++) {
+                    const int c = g / d.kernel[0], ky = g % d.kernel[0];
+                    tab[g].offset = g < row_groups ? (c * d.height + ky) * d.width : 0;
+                    tab[g].tap = g < row_groups ? ky : ROW_PADDING;
+                }
+            }
             DLP_CUDA_OK(cudaMalloc((void **)&plan->ktab, sizeof(KTap) * k_pad));
             cudaError_t e = cudaMalloc((void **)&plan->tap_dydx, sizeof(int) * taps.size());
             if(e == cudaSuccess) e = cudaMemcpy(plan->ktab, tab.data(), sizeof(KTap) * k_pad, cudaMemcpyHostToDevice);
@@ -278,7 +292,7 @@ dlp_status dlp_conv2d_fwd_prepack(const dlp_conv2d_plan *plan, const float *w, v
     for(int g = 0; g < plan->d.groups; g++) {
         dlp_status st = tc_prepack(plan->packed, w + (long long)g * cout_g * plan->k, plan->k, 1, cout_g, plan->k,
                                    static_cast<float *>(packed) + g * (plan->packed.bytes() / sizeof(float)),
-                                   plan->tapblock ? plan->num_taps : 0, (cudaStream_t)stream);
+                                   plan->tapblock ? plan->num_taps : 0, (cudaStream_t)stream, 1, 0, plan->rowtaps ? plan->d.kernel[1] : 0);
         if(st != DLP_OK) return st;
     }
     return DLP_OK;
@@ -331,7 +345,7 @@ static dlp_status conv_enqueue(const dlp_conv2d_plan *plan, const float *x, cons
         p.a_k_stride = (long long)d.height * d.width;
     }
     else {
-        p.a_mode = plan->tapblock ? A_TAPBLOCK : A_GATHER;
+        p.a_mode = plan->tapblock ? A_TAPBLOCK : (plan->rowtaps ? A_ROWTAPS : A_GATHER);
         p.a_k_stride = (long long)d.height * d.width;
         p.ktab = plan->ktab;
         p.tap_dydx = plan->tap_dydx;

@@ -15,8 +15,11 @@ namespace dlp {
 enum : int {
     A_GATHER = 0,  // general convolution: address = row_base + ktab[k].offset, bounds-checked per tap
     A_STRIDED = 1, // address = row_base + k * a_k_stride (1x1 stride-1 convolution, matrices)
-    A_TAPBLOCK = 2 // convolution with channels in blocks of 32: k-block kb = (channel block, tap); the 32 values
+    A_TAPBLOCK = 2, // convolution with channels in blocks of 32: k-block kb = (channel block, tap); the 32 values
                    // of a k-block are one tap of 32 consecutive channels: row_base + tap offset + channel * a_k_stride
+    A_ROWTAPS = 3  // convolution with few input channels and a wide kernel (a 7x7 stem): the reduction index is
+                   // (channel, kernel row, kernel column padded to 8), so a k-block is four kernel rows of eight
+                   // consecutive input elements each: one table entry and one row test per eight loads (tensor-core kernel only)
 };
 enum : int {
     OUT_NCHW = 0,     // row = (b, pix): y[(b * out_channels_total + col) * out_plane + pix]
@@ -28,7 +31,10 @@ struct KTap {
     int offset;  // element offset of reduction index k from the row's base address: c*H*W + dy*W + dx
     int tap;     // FFMA kernel: the kernel tap ky*KW + kx.  Tensor-core kernel: (ky << 8) | kx, and
                  // TAP_PADDING for the zero padding beyond K (a kernel row that never exists)
+                 // A_ROWTAPS: one entry per (channel, kernel row): offset of its first column, tap = ky (ROW_PADDING beyond K)
 };
+constexpr int ROW_PADDING = 31;
+constexpr int ROWTAPS_WIDTH = 8;      // kernel columns per (channel, kernel row) group in the A_ROWTAPS order
 constexpr int TAP_PADDING = 31 << 8;
 constexpr int MAX_KERNEL_SIDE = 30;   // larger kernels (more rows or columns than validity bits) use the FFMA path
 
@@ -137,8 +143,9 @@ struct TcPacked {
 TcPacked tc_packed_layout(int cols, int k);
 // taps > 0 packs in the A_TAPBLOCK order: packed k = ((channel block * taps + tap) * 32 + channel in block)
 // batch > 1: that many matrices b_batch_stride elements apart, packed one after the other (L.bytes() each)
+// row_kw > 0 packs in the A_ROWTAPS order: packed k = (channel * KH + ky) * 8 + kx  <-  source k = (channel * KH + ky) * row_kw + kx
 dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
-                      float *packed, int taps, cudaStream_t stream, int batch = 1, long long b_batch_stride = 0);
+                      float *packed, int taps, cudaStream_t stream, int batch = 1, long long b_batch_stride = 0, int row_kw = 0);
 // A batch of equal-sized products in one launch: matrix i reads a + i * a_stride, its own packed operand and writes y + i * y_stride.
 struct TcBatch {
     int count = 1;

@@ -184,7 +184,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    if(MODE == A_GATHER)
+    if(MODE == A_GATHER || MODE == A_ROWTAPS)
         for(int i = threadIdx.x; i < ktab_smem_entries / 2; i += NUM_THREADS) ktab_s[i] = __ldg(reinterpret_cast<const int4 *>(p.ktab) + i);
     tc_fence_before();
     __syncthreads();
@@ -527,7 +527,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 r = make_row(p, (loaded_row_tile / n_tiles) * BM + row_in_tile, a_off, y_off);
                 if(TC_DIAG(DIAG_NO_A_LOADS)) r.valid = false;
                 row_mask = col_mask = 0;
-                if(MODE == A_GATHER && r.valid) {
+                if((MODE == A_GATHER || MODE == A_ROWTAPS) && r.valid) {
                     for(int ky = 0; ky < p.kh; ky++)
                         if(unsigned(r.iy0 + ky * p.dil_h) < unsigned(p.in_h)) row_mask |= 1u << ky;
                     for(int kx = 0; kx < p.kw; kx++)
@@ -572,6 +572,19 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 else {
                     #pragma unroll
                     for(int i = 0; i < BK; i++) buf[i] = 0.0f;
+                }
+            }
+            else if(MODE == A_ROWTAPS) {
+                // four (channel, kernel row) groups of eight consecutive input elements; the table (always in shared
+                // memory) gives a group's offset and its kernel row, whose validity bit gates the group's column bits
+                const int2 *tab = reinterpret_cast<const int2 *>(ktab_s) + kb_all * (BK / ROWTAPS_WIDTH);
+                #pragma unroll
+                for(int g = 0; g < BK / ROWTAPS_WIDTH; g++) {
+                    const int2 e = tab[g];
+                    const float *src = p.a + r.base + e.x;
+                    const unsigned cols = ((row_mask >> e.y) & 1u) ? col_mask : 0u;
+                    #pragma unroll
+                    for(int kx = 0; kx < ROWTAPS_WIDTH; kx++) buf[g * ROWTAPS_WIDTH + kx] = (cols >> kx) & 1u ? __ldg(src + kx) : 0.0f;
                 }
             }
             else {
@@ -699,14 +712,15 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
 // 16-byte store per tile.  n_major: consecutive threads take consecutive columns (sources whose columns are contiguous),
 // otherwise consecutive chunks along k (sources whose k is contiguous, read 16 bytes at a time when aligned).
 __global__ void prepack_kernel(const float *__restrict__ b, long long col_stride, long long k_stride, int cols, int k,
-                               int n_pad, int k_pad, int bn, int taps, float *__restrict__ packed, long long b_batch_stride, int n_major)
+                               int n_pad, int k_pad, int bn, int taps, float *__restrict__ packed, long long b_batch_stride, int n_major,
+                               int row_kw)
 {
     const int chunks = k_pad / 4;
     const long long total = (long long)n_pad * chunks;
     b += blockIdx.y * b_batch_stride;           // a batch of matrices: blockIdx.y picks one, packed one after the other
     packed += blockIdx.y * (2ll * n_pad * k_pad);
     const int kblocks = k_pad / BK;
-    const bool vec = !n_major && taps == 0 && k_stride == 1 && (col_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0;
+    const bool vec = !n_major && taps == 0 && row_kw == 0 && k_stride == 1 && (col_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(b) & 15) == 0;
     for(long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
         int n, c;
         if(n_major) { c = int(idx / n_pad); n = int(idx - (long long)c * n_pad); }
@@ -727,7 +741,14 @@ __global__ void prepack_kernel(const float *__restrict__ b, long long col_stride
                         const int cb = kb / taps, t = kb % taps;
                         ks = (cb * BK + i + j) * taps + t;
                     }
-                    if(kk + j < k) v[j] = __ldg(b + n * col_stride + ks * k_stride);
+                    bool exists = kk + j < k;
+                    if(row_kw > 0) {
+                        // packed order (channel, kernel row, column padded to 8) <- source order (channel, kernel row, column)
+                        const int g = (kk + j) / ROWTAPS_WIDTH, kx = (kk + j) % ROWTAPS_WIDTH;
+                        ks = g * row_kw + kx;
+                        exists = kx < row_kw && ks < k;
+                    }
+                    if(exists) v[j] = __ldg(b + n * col_stride + ks * k_stride);
                 }
             }
         }
@@ -774,14 +795,14 @@ TcPacked tc_packed_layout(int cols, int k)
 }
 
 dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride, long long b_k_stride, int cols, int k,
-                      float *packed, int taps, cudaStream_t stream, int batch, long long b_batch_stride)
+                      float *packed, int taps, cudaStream_t stream, int batch, long long b_batch_stride, int row_kw)
 {
     const long long total = (long long)L.n_pad * (L.k_pad / 4);
     const int threads = 256;
     const int blocks = int(std::min<long long>(ceil_div<long long>(total, threads), 8 * sm_count()));
     if(batch < 1 || batch > 65535) return fail(DLP_INVALID_ARGUMENT, "a batched product takes 1 to 65535 matrices");
     tc::prepack_kernel<<<dim3(blocks, batch), threads, 0, stream>>>(b, b_col_stride, b_k_stride, cols, k, L.n_pad, L.k_pad, L.bn, taps, packed,
-                                                                    b_batch_stride, b_col_stride == 1 && b_k_stride != 1 ? 1 : 0);
+                                                                    b_batch_stride, b_col_stride == 1 && b_k_stride != 1 ? 1 : 0, row_kw);
     DLP_LAUNCH_OK("prepack_kernel");
     return DLP_OK;
 }
@@ -812,7 +833,9 @@ dlp_status launch_bn(const Contraction &p, const TcPacked &L, const float *packe
                      const TcBatch &batch)
 {
     // the gather table rides along in shared memory when it is at most 8 KB (1024 entries: K up to 1024)
-    const int ktab_entries = MODE == A_GATHER && L.k_pad <= 1024 && p.ktab != nullptr ? L.k_pad : 0;
+    // (row-taps mode: one entry per eight k, always in shared memory; the plan keeps it within 1024 entries)
+    const int ktab_entries = MODE == A_ROWTAPS ? L.k_pad / ROWTAPS_WIDTH : (MODE == A_GATHER && L.k_pad <= 1024 && p.ktab != nullptr ? L.k_pad : 0);
+    if(MODE == A_ROWTAPS && (p.ktab == nullptr || ktab_entries > 1024)) return fail(DLP_INVALID_ARGUMENT, "row-taps table missing or too long");
     const int smem = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int((sizeof(tc::Shared) + 15) & ~size_t(15)) + ktab_entries * 8;
     const int smem_max = 1024 + tc::STAGES * 2 * BN * tc::BK * 4 + BN * tc::BM * 4 + int((sizeof(tc::Shared) + 15) & ~size_t(15)) + 1024 * 8;
     {
@@ -908,6 +931,9 @@ dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const 
     case 128 * 4 + A_GATHER: st = launch_bn<128, A_GATHER>(q, L, packed, stream, splits, split_stride, batch); break;
     case 128 * 4 + A_STRIDED: st = launch_bn<128, A_STRIDED>(q, L, packed, stream, splits, split_stride, batch); break;
     case 128 * 4 + A_TAPBLOCK: st = launch_bn<128, A_TAPBLOCK>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 32 * 4 + A_ROWTAPS: st = launch_bn<32, A_ROWTAPS>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 64 * 4 + A_ROWTAPS: st = launch_bn<64, A_ROWTAPS>(q, L, packed, stream, splits, split_stride, batch); break;
+    case 128 * 4 + A_ROWTAPS: st = launch_bn<128, A_ROWTAPS>(q, L, packed, stream, splits, split_stride, batch); break;
     default: return fail(DLP_INVALID_ARGUMENT, "unsupported column tile");
     }
     if(st != DLP_OK || splits == 1) return st;

@@ -107,6 +107,69 @@ __global__ void pooling2d_band_kernel(const float *__restrict__ x, float *__rest
     }
 }
 
+// Max pooling 3x3, stride 2, padding 1 over rows of even width, without shared memory: a warp takes 32 output columns
+// of a strip of RS output rows.  A lane reads the two input columns 2*oc and 2*oc+1 of every input row of the strip as one
+// aligned 8-byte load (a warp reads 256 consecutive bytes), takes column 2*oc-1 from its left neighbour by shuffle, and
+// keeps the row maxima in registers; all the strip's loads are issued before the first is used.  Maximum is exact in any
+// order, so the result is bit-identical to pooling2d_kernel's.
+template<int RS>
+__global__ void __launch_bounds__(256) pool_max3s2_kernel(const float *__restrict__ x, float *__restrict__ y, long long items, int col_blocks,
+                                                          int strips, int in_h, int in_w, int out_h, int out_w)
+{
+    const long long item = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if(item >= items) return;
+    const int cb = int(item % col_blocks);
+    const long long t = item / col_blocks;
+    const int strip = int(t % strips);
+    const long long plane = t / strips;
+    const int oc = cb * 32 + lane, orow0 = strip * RS;
+    const bool col_ok = oc < out_w;
+    const float *src = x + plane * (long long)in_h * in_w;
+    constexpr int ROWS = 2 * RS + 1;
+    float2 a[ROWS];
+    float left[ROWS];
+    #pragma unroll
+    for(int r = 0; r < ROWS; r++) {
+        const int iy = 2 * orow0 - 1 + r;
+        const bool ok = col_ok && iy >= 0 && iy < in_h;
+        a[r] = ok ? __ldg(reinterpret_cast<const float2 *>(src + (long long)iy * in_w) + oc) : make_float2(-FLT_MAX, -FLT_MAX);
+        // lane 0 has no left neighbour in the warp: column 2*oc-1 is the padding (first block) or one more load
+        left[r] = (ok && lane == 0 && oc > 0) ? __ldg(src + (long long)iy * in_w + 2 * oc - 1) : -FLT_MAX;
+    }
+    float h[ROWS];
+    #pragma unroll
+    for(int r = 0; r < ROWS; r++) {
+        const float from_lane = __shfl_up_sync(0xffffffffu, a[r].y, 1);
+        const float l = lane == 0 ? left[r] : from_lane;
+        h[r] = fmaxf(fmaxf(l, a[r].x), a[r].y);
+    }
+    float *dst = y + plane * (long long)out_h * out_w + oc;
+    #pragma unroll
+    for(int j = 0; j < RS; j++)
+        if(col_ok && orow0 + j < out_h) dst[(long long)(orow0 + j) * out_w] = fmaxf(fmaxf(h[2 * j], h[2 * j + 1]), h[2 * j + 2]);
+}
+
+// Global pooling of small odd-sized planes: a CTA of 128 threads copies 128 consecutive planes into shared memory with
+// coalesced 16-byte loads, then thread t reduces plane t in index order (odd plane size: conflict-free).
+__global__ void __launch_bounds__(128) global_pooling_tile_kernel(const float *__restrict__ x, float *__restrict__ y, int planes, int plane_size,
+                                                                  int mode_avg)
+{
+    extern __shared__ float tile[];
+    const int plane0 = blockIdx.x * 128, count = min(128, planes - plane0) * plane_size;
+    const float *src = x + (long long)plane0 * plane_size;           // 128 * plane_size * 4 bytes per CTA: 16-byte aligned when x is
+    const float4 *src4 = reinterpret_cast<const float4 *>(src);
+    float4 *tile4 = reinterpret_cast<float4 *>(tile);
+    for(int i = threadIdx.x; i < count / 4; i += 128) tile4[i] = __ldg(src4 + i);
+    for(int i = (count & ~3) + threadIdx.x; i < count; i += 128) tile[i] = __ldg(src + i);
+    __syncthreads();
+    if(plane0 + int(threadIdx.x) >= planes) return;
+    const float *mine = tile + threadIdx.x * plane_size;
+    float v = mode_avg ? 0.0f : -FLT_MAX;
+    for(int i = 0; i < plane_size; i++) v = mode_avg ? v + mine[i] : fmaxf(v, mine[i]);
+    y[plane0 + threadIdx.x] = mode_avg ? v * (1.0f / plane_size) : v;
+}
+
 // one warp per plane
 __global__ void global_pooling_kernel(const float *__restrict__ x, float *__restrict__ y, int planes, int plane_size, int mode_avg)
 {
@@ -247,6 +310,16 @@ dlp_status dlp_pooling2d_fwd(const float *x, float *y, int planes, int in_h, int
     DLP_REQUIRE(mode == 0 || mode == 1, "mode must be 0 (max) or 1 (avg)");
     const long long total = (long long)planes * oh * ow;
     if(total <= 0) return DLP_OK;
+    if(mode == 0 && kernel[0] == 3 && kernel[1] == 3 && stride[0] == 2 && stride[1] == 2 && pad[0] == 1 && pad[1] == 1 && in_w % 2 == 0 &&
+       2 * ow <= in_w && reinterpret_cast<uintptr_t>(x) % 8 == 0) {
+        constexpr int RS = 8;
+        const int col_blocks = ceil_div(ow, 32), strips = ceil_div(oh, RS);
+        const long long items = (long long)planes * col_blocks * strips;
+        pool_max3s2_kernel<RS><<<unsigned(ceil_div<long long>(items, 8)), 256, 0, (cudaStream_t)stream>>>(x, y, items, col_blocks, strips, in_h, in_w,
+                                                                                                         oh, ow);
+        DLP_LAUNCH_OK("pool_max3s2_kernel");
+        return DLP_OK;
+    }
     // Bands of output rows through shared memory when a useful band fits in 12 KB: each input byte is read
     // from memory once (plus the halo rows between bands), in full lines.
     {
@@ -284,6 +357,12 @@ dlp_status dlp_global_pooling_fwd(const float *x, float *y, int planes, int plan
     DLP_REQUIRE(x && y, "null tensor");
     DLP_REQUIRE(plane_size > 0 && (mode == 0 || mode == 1), "bad global pooling arguments");
     if(planes <= 0) return DLP_OK;
+    if(plane_size % 2 == 1 && plane_size <= 95 && reinterpret_cast<uintptr_t>(x) % 16 == 0) {
+        global_pooling_tile_kernel<<<ceil_div(planes, 128), 128, size_t(128) * plane_size * sizeof(float), (cudaStream_t)stream>>>(x, y, planes,
+                                                                                                                                plane_size, mode);
+        DLP_LAUNCH_OK("global_pooling_tile_kernel");
+        return DLP_OK;
+    }
     const int threads = 256, warps_per_block = threads / 32;
     global_pooling_kernel<<<ceil_div(planes, warps_per_block), threads, 0, (cudaStream_t)stream>>>(x, y, planes, plane_size, mode);
     DLP_LAUNCH_OK("global_pooling_kernel");

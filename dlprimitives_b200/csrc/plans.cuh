@@ -18,6 +18,7 @@ struct dlp_conv2d_plan {
     bool strided_a;          // 1x1, stride 1, no padding: the taps are a plain stride
     bool winograd_tc = false; // CK_WINOGRAD: the sixteen products run on the tensor cores (winograd_tc.cu), not as fp32 FMA
     bool tapblock;           // tensor-core path with channels in blocks of 32: K runs (channel block, tap, channel)
+    bool rowtaps = false;    // tensor-core path for wide kernels over few channels: K runs (channel, kernel row, column padded to 8)
     TcPacked packed;
     KTap *ktab = nullptr;    // device, k_pad entries (gather mode)
     int *tap_dydx = nullptr; // device, one entry per kernel tap

@@ -400,3 +400,40 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_device_usable()
     plan.enqueue(to_dev(x), to_dev(w), None, y, ws)
     assert rel_err(y.cpu().numpy(), ob.conv2d(x, w, None, pad=1, activation="relu")) <= REL_TOL
     assert capi.device_status() == 0
+
+
+ROWTAPS_CASES = [
+    # N, Cin, H, W, Cout, kernel, stride, pad, groups
+    (3, 3, 37, 45, 64, 7, 2, 3, 1),            # the stem's geometry on an odd-sized image
+    (2, 5, 19, 23, 40, 5, 1, 2, 1),            # 5 columns padded to 8, ragged column tile
+    (2, 3, 21, 21, 130, (3, 8), (1, 2), (1, 0), 1),   # 8 columns exactly, non-square, two column tiles
+    (4, 1, 30, 30, 16, (7, 6), 1, (0, 5), 1),  # one channel: fewer row groups than a k-block; padding wider than the image edge
+    (2, 48, 12, 12, 32, 5, 1, 2, 2),           # groups of 24 channels: 120 row groups
+    (1, 200, 9, 9, 24, 7, 1, 3, 1),            # 1400 row groups: beyond the table, falls back to the gather loaders
+]
+
+
+@pytest.mark.parametrize("case", ROWTAPS_CASES, ids=[str(i) for i in range(len(ROWTAPS_CASES))])
+def test_row_taps_loader(case):
+    """Wide kernels over channel counts that are not blocks of 32: the reduction runs (channel, kernel row, column
+    padded to 8).  Compared with the CPU checker; every case names the kernel it expects."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    N, cin, H, W, cout, k, stride, pad, groups = case
+    rng = np.random.default_rng(cin * 1000 + H)
+    kh, kw = (k, k) if isinstance(k, int) else k
+    x = rng.standard_normal((N, cin, H, W), dtype=np.float32)
+    w = kaiming(rng, (cout, cin // groups, kh, kw))
+    b = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+    plan = capi.Conv2DForward(channels_in=cin, channels_out=cout, kernel=k, stride=stride, pad=pad, groups=groups, batch=N, height=H,
+                              width=W, bias=True, activation="relu")
+    expect = "_gather" if cin // groups * kh > 1024 else "_rowtaps"
+    assert plan.kernel().endswith(expect), plan.kernel()
+    y = torch.full(plan.output_shape(N), float("nan"), device=DEV)
+    ws = torch.empty(max(plan.workspace(), 16), dtype=torch.uint8, device=DEV)
+    plan.enqueue(to_dev(x), to_dev(w), to_dev(b), y, ws)
+    assert capi.device_status() == 0
+    want = ob.conv2d(x, w, b, stride=stride, pad=pad, groups=groups, activation="relu")
+    got = y.cpu().numpy()
+    assert got.shape == want.shape and not np.isnan(got).any()
+    assert rel_err(got, want) <= REL_TOL, (plan.kernel(), rel_err(got, want))

@@ -66,3 +66,24 @@ def test_large_shapes_against_checker():
     assert rel_err(got, ob.batchnorm_inference(a, mean, var, gamma, beta)) <= 1e-6
     got, = run("BatchNorm", {"features": 64, "affine": False}, [a], [mean, var])
     assert rel_err(got, ob.batchnorm_inference(a, mean, var)) <= 1e-6
+
+
+@pytest.mark.parametrize("shape", [(3, 5, 30, 70), (1, 2, 7, 6), (2, 3, 113, 200), (1, 1, 2, 2)])
+def test_max_pool_3x3_stride2_ragged_shapes(shape):
+    """The register kernel for max 3x3 / stride 2 / pad 1 over even widths: strips and column blocks that end inside
+    the plane, odd heights, a single window.  Bit-exact against the checker."""
+    from oracle import bindings as ob
+    x = np.random.default_rng(sum(shape)).standard_normal(shape, dtype=np.float32)
+    got, = run("Pooling2D", {"mode": "max", "kernel": 3, "stride": 2, "pad": 1}, [x])
+    assert np.array_equal(got, ob.pooling2d(x, 3, 2, 1, "max"))
+
+
+@pytest.mark.parametrize("shape", [(3, 50, 5, 5), (1, 7, 3, 3), (2, 129, 7, 7), (1, 3, 9, 9), (2, 5, 4, 4)])
+def test_global_pooling_plane_counts(shape):
+    """Plane counts that do not fill the last CTA of the tiled kernel (odd plane sizes) and an even plane size (the
+    warp-per-plane kernel)."""
+    from oracle import bindings as ob
+    x = np.random.default_rng(sum(shape)).standard_normal(shape, dtype=np.float32)
+    for mode in ("avg", "max"):
+        got, = run("GlobalPooling", {"mode": mode}, [x])
+        assert rel_err(got, ob.global_pooling(x, mode)) <= 1e-6
