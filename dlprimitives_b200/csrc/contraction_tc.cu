@@ -61,7 +61,7 @@ enum { ST_TMA_EMPTY = 101, ST_MMA_FULL_B = 102, ST_MMA_FULL_A = 103, ST_MMA_ACC 
 // Diagnostics are compiled in only with -DDLP_TC_DIAGNOSTICS (the hot loops are tight and share a small
 // instruction cache): the timeline (environment variable DLP_TC_TRACE=<file>) and the switches below
 // (environment variable DLP_TC_DIAG, for timing experiments; results are wrong with any set).
-enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4 };
+enum { DIAG_NO_A_LOADS = 1, DIAG_NO_STORES = 2, DIAG_NO_MMA = 4, DIAG_NO_BIAS_LOADS = 8, DIAG_NO_RESIDUAL_LOADS = 16, DIAG_LEAN_NO_STG = 32 };
 
 struct Shared {
     unsigned long long full_b[STAGES];         // the bulk copy of a k-block's B tiles landed
@@ -80,18 +80,18 @@ struct Shared {
 // Lean store of N output columns of one row: y = clamp(acc + bias) [then clamp(y + s*residual)].
 template<int N, bool BIAS, bool RES>
 __device__ __forceinline__ void store_cols(const float (&v)[N], float *y0, const float (&res)[N], long long cs, const float *b0,
-                                           float2 clamp, float res_scale, float2 post_clamp)
+                                           float2 clamp, float res_scale, float2 post_clamp, bool no_bias_loads = false, bool no_stg = false)
 {
     #pragma unroll
     for(int j = 0; j < N; j++) {
         float a = v[j];
-        if(BIAS) a += __ldg(b0 + j);
+        if(BIAS) a += no_bias_loads ? 0.25f : __ldg(b0 + j);
         a = fminf(fmaxf(a, clamp.x), clamp.y);
         if(RES) {
             a = a + res_scale * res[j];
             a = fminf(fmaxf(a, post_clamp.x), post_clamp.y);
         }
-        *y0 = a;
+        if(!no_stg || a == 12345.678f) *y0 = a;
         y0 += cs;
     }
 }
@@ -447,7 +447,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                         // the residual operand of these columns travels while the tensor-memory load does
                         const float *rp = res_row + (long long)(g * G) * col_stride;
                         #pragma unroll
-                        for(int j = 0; j < G; j++) { res[j] = __ldg(rp); rp += col_stride; }
+                        for(int j = 0; j < G; j++) { res[j] = TC_DIAG(DIAG_NO_RESIDUAL_LOADS) ? 0.5f : __ldg(rp); rp += col_stride; }
                     }
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if(warp == WARP_ACC0 && lane == 0) TC_TRACE(10, chunk * GROUPS + g);
@@ -472,12 +472,12 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                         float *y0 = y_row + (long long)(g * G) * col_stride;
                         const float *b0 = p.bias + col0;
                         if(with_res) {
-                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp);
-                            else store_cols<G, false, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp);
+                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp, TC_DIAG(DIAG_NO_BIAS_LOADS), TC_DIAG(DIAG_LEAN_NO_STG));
+                            else store_cols<G, false, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp, TC_DIAG(DIAG_NO_BIAS_LOADS), TC_DIAG(DIAG_LEAN_NO_STG));
                         }
                         else {
-                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp);
-                            else store_cols<G, false, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp);
+                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp, TC_DIAG(DIAG_NO_BIAS_LOADS), TC_DIAG(DIAG_LEAN_NO_STG));
+                            else store_cols<G, false, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp, TC_DIAG(DIAG_NO_BIAS_LOADS), TC_DIAG(DIAG_LEAN_NO_STG));
                         }
                     }
                     else {
@@ -808,15 +808,17 @@ dlp_status tc_prepack(const TcPacked &L, const float *b, long long b_col_stride,
 }
 
 namespace {
-// How many equal parts to cut K into.  Time is counted in k-block periods: a CTA works through
+// How many equal parts to cut K into.  Time is counted in k-block periods (about 0.6 us): a CTA works through
 // ceil(items / SMs) work items of (k-blocks per part + a fixed cost for pipeline fill and epilogue) each,
 // and a split run pays for the finishing kernel.  K is cut only when that model gains a tenth or more.
+// The two constants are fitted to timings of batch-32 layer shapes with forced splits (52 to 196 tiles of 16 to 144
+// k-blocks): 7 periods per work item, 20 for the second launch and its pass over the partial sums.
 int choose_splits(long long rows, const TcPacked &L)
 {
     const long long tiles = ceil_div<long long>(rows, tc::BM) * (L.n_pad / L.bn);
     const int kb = L.k_pad / tc::BK, sms = sm_count();
     if(tiles <= 0 || tiles > 4 * sms || kb < 8) return 1;
-    const double item_fixed = 6.0, finish = 10.0;
+    const double item_fixed = 7.0, finish = 20.0;
     const double uncut = double(ceil_div<long long>(tiles, sms)) * (kb + item_fixed);
     int best = 1;
     double best_cost = 0.9 * uncut;

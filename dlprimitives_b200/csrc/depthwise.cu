@@ -174,6 +174,88 @@ __global__ void __launch_bounds__(THREADS) depthwise_kernel(DwParams p)
     }
 }
 
+
+// 3x3, padding 1, even widths: the register kernel.  No shared memory and no phases: a lane owns V consecutive input
+// columns (V = 4 or 2: one 16- or 8-byte load per input row) of one plane over a strip of RS output rows, takes the
+// column to its left (and, at stride 1, to its right) from the neighbouring lane by shuffle -- lanes run over (plane,
+// column group), and a column group at the edge of a row gets the zero padding instead, so nothing crosses from one plane
+// to the next -- and issues all the loads of its strip before the first use.  Per output the products are added in the
+// same order (ky, then kx) as in depthwise_kernel; a tap in the padding contributes fmaf(0, w, acc) = acc.
+template<int S, int V>
+__global__ void __launch_bounds__(THREADS) depthwise3_reg_kernel(DwParams p, long long groups, int qw, int strips)
+{
+    constexpr int RS = S == 1 ? 6 : 4;        // output rows per strip
+    constexpr int RI = S * (RS - 1) + 3;      // input rows a strip reads
+    constexpr int VO = V / S;                 // outputs per lane and row
+    const unsigned full = 0xffffffffu;
+    const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if(wid >= ((groups + 31) / 32) * strips) return;
+    const int r0 = int(wid % strips) * RS;
+    const long long g = (wid / strips) * 32 + lane;
+    const bool valid = g < groups;
+    const long long pl = valid ? g / qw : 0;
+    const int c = valid ? int(g - pl * qw) : 0;
+    const int ch = int(pl % p.channels);
+    const float *xin = p.x + pl * ((long long)p.H * p.W) + c * V;
+    float w[9];
+    #pragma unroll
+    for(int i = 0; i < 9; i++) w[i] = valid ? __ldg(p.w + ch * 9 + i) : 0.0f;
+
+    float in[RI][V + 2];     // [0]: the column to the left, [1..V]: the lane's own, [V+1]: the column to the right (stride 1)
+    bool ok[RI];
+    #pragma unroll
+    for(int i = 0; i < RI; i++) {
+        const int iy = S * r0 - 1 + i;
+        ok[i] = valid && iy >= 0 && iy < p.H;
+        const float *row = xin + (long long)iy * p.W;
+        if(V == 4) {
+            const float4 t = ok[i] ? __ldg(reinterpret_cast<const float4 *>(row)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            in[i][1] = t.x; in[i][2] = t.y; in[i][3] = t.z; in[i][4] = t.w;
+        }
+        else {
+            const float2 t = ok[i] ? __ldg(reinterpret_cast<const float2 *>(row)) : make_float2(0.0f, 0.0f);
+            in[i][1] = t.x; in[i][2] = t.y;
+        }
+        // the first and the last lane of the warp have their neighbour in another warp: one more load
+        in[i][0] = (ok[i] && lane == 0 && c > 0) ? __ldg(row - 1) : 0.0f;
+        in[i][V + 1] = (S == 1 && ok[i] && lane == 31 && c < qw - 1) ? __ldg(row + V) : 0.0f;
+    }
+    #pragma unroll
+    for(int i = 0; i < RI; i++) {
+        const float from_left = __shfl_up_sync(full, in[i][V], 1), from_right = __shfl_down_sync(full, in[i][1], 1);
+        if(lane > 0) in[i][0] = c > 0 ? from_left : 0.0f;
+        if(S == 1 && lane < 31) in[i][V + 1] = c < qw - 1 ? from_right : 0.0f;
+    }
+    if(!valid) return;
+    const float b = p.bias ? __ldg(p.bias + ch) : 0.0f;
+    float *yrow = p.y + pl * ((long long)p.OH * p.OW) + c * VO;
+    #pragma unroll
+    for(int j = 0; j < RS; j++) {
+        const int oy = r0 + j;
+        if(oy >= p.OH) break;
+        float o[VO];
+        #pragma unroll
+        for(int t = 0; t < VO; t++) {
+            float acc = 0.0f;
+            #pragma unroll
+            for(int ky = 0; ky < 3; ky++)
+                #pragma unroll
+                for(int kx = 0; kx < 3; kx++) acc = fmaf(in[S * j + ky][S * t + kx], w[ky * 3 + kx], acc);
+            if(p.bias) acc += b;
+            o[t] = apply_act(acc, p.act);
+        }
+        float *dst = yrow + (long long)oy * p.OW;
+        if(p.factor != 0.0f) {
+            #pragma unroll
+            for(int t = 0; t < VO; t++) o[t] += p.factor * dst[t];
+        }
+        if(VO == 4) *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[VO - 1]);
+        else if(VO == 2) *reinterpret_cast<float2 *>(dst) = make_float2(o[0], o[VO - 1]);
+        else dst[0] = o[0];
+    }
+}
+
 } // namespace
 
 bool depthwise_supported(int ks_h, int ks_w, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int in_w)
@@ -197,6 +279,21 @@ dlp_status launch_depthwise(const float *x, const float *w, const float *bias, f
     p.planes = batch * channels;
     p.act = act; p.factor = factor;
     if(p.planes <= 0 || p.OH <= 0 || p.OW <= 0) return DLP_OK;
+    if(ks == 3 && pad == 1 && W % 2 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+        const int v = W % 4 == 0 ? 4 : 2;
+        const int qw = W / v, rs = stride == 1 ? 6 : 4;
+        const long long groups = (long long)p.planes * qw;
+        const int strips = ceil_div(p.OH, rs);
+        const long long warps = ceil_div<long long>(groups, 32) * strips;
+        const long long blocks = ceil_div<long long>(warps, THREADS / 32);
+        if(blocks > 0x7fffffffLL) return fail(DLP_INVALID_ARGUMENT, "depthwise problem too large for one launch");
+        if(stride == 1 && v == 4) depthwise3_reg_kernel<1, 4><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips);
+        else if(stride == 1) depthwise3_reg_kernel<1, 2><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips);
+        else if(v == 4) depthwise3_reg_kernel<2, 4><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips);
+        else depthwise3_reg_kernel<2, 2><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips);
+        DLP_LAUNCH_OK("depthwise3_reg_kernel");
+        return DLP_OK;
+    }
     const long long plane_elems = (long long)H * W;
     const int budget = SMEM_FLOATS - 8;
     if(plane_elems <= budget) {

@@ -437,3 +437,29 @@ def test_row_taps_loader(case):
     got = y.cpu().numpy()
     assert got.shape == want.shape and not np.isnan(got).any()
     assert rel_err(got, want) <= REL_TOL, (plan.kernel(), rel_err(got, want))
+
+
+@pytest.mark.parametrize("case", [(2, 5, 9, 12, 1), (3, 7, 15, 14, 2), (1, 3, 6, 8, 2), (2, 4, 5, 6, 1), (1, 33, 7, 10, 2), (2, 40, 20, 36, 1),
+                                  (1, 6, 7, 7, 1)],
+                         ids=lambda c: "x".join(str(v) for v in c))
+def test_depthwise_3x3_register_kernel(case):
+    """Depthwise 3x3 / pad 1 at stride 1 and 2 over even widths (16- and 8-byte loads, halo by shuffle), odd heights, lane
+    counts that do not fill the last warp, bias + ReLU6, and y = factor*y + ...; the odd width takes the staged kernel."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    N, C, H, W, stride = case
+    rng = np.random.default_rng(N * 100 + C)
+    x = rng.standard_normal((N, C, H, W), dtype=np.float32)
+    w = kaiming(rng, (C, 1, 3, 3))
+    b = rng.uniform(-0.5, 0.5, C).astype(np.float32)
+    plan = capi.Conv2DForward(channels_in=C, channels_out=C, kernel=3, stride=stride, pad=1, groups=C, batch=N, height=H, width=W,
+                              bias=True, activation="relu6")
+    assert plan.algo() == "depthwise_separable"
+    want = ob.conv2d(x, w, b, stride=stride, pad=1, groups=C, activation="relu6")
+    y0 = rng.standard_normal(want.shape).astype(np.float32)
+    for factor in (0.0, 0.5):
+        y = to_dev(y0) if factor else torch.full(plan.output_shape(N), float("nan"), device=DEV)
+        plan.enqueue(to_dev(x), to_dev(w), to_dev(b), y, None, factor=factor)
+        got = y.cpu().numpy()
+        assert got.shape == want.shape
+        assert rel_err(got, want + factor * y0) <= REL_TOL, (case, factor)
