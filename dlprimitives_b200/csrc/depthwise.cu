@@ -181,10 +181,11 @@ __global__ void __launch_bounds__(THREADS) depthwise_kernel(DwParams p)
 // column group), and a column group at the edge of a row gets the zero padding instead, so nothing crosses from one plane
 // to the next -- and issues all the loads of its strip before the first use.  Per output the products are added in the
 // same order (ky, then kx) as in depthwise_kernel; a tap in the padding contributes fmaf(0, w, acc) = acc.
-template<int S, int V>
+// RS: output rows per strip -- 6 at stride 1, 4 at stride 2, and 7 for stride-2 planes of up to 7 output rows (one strip,
+// no input row read twice).
+template<int S, int V, int RS>
 __global__ void __launch_bounds__(THREADS) depthwise3_reg_kernel(DwParams p, long long groups, int qw, int strips)
 {
-    constexpr int RS = S == 1 ? 6 : 4;        // output rows per strip
     constexpr int RI = S * (RS - 1) + 3;      // input rows a strip reads
     constexpr int VO = V / S;                 // outputs per lane and row
     const unsigned full = 0xffffffffu;
@@ -279,18 +280,27 @@ dlp_status launch_depthwise(const float *x, const float *w, const float *bias, f
     p.planes = batch * channels;
     p.act = act; p.factor = factor;
     if(p.planes <= 0 || p.OH <= 0 || p.OW <= 0) return DLP_OK;
+    // (measured on the MobileNetV2 rows: odd widths -- 4-byte loads -- and whole 14-row planes as one strip at stride 1
+    // are no faster than the staged kernel or the 6-row strips, so those variants are not kept)
     if(ks == 3 && pad == 1 && W % 2 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
         const int v = W % 4 == 0 ? 4 : 2;
-        const int qw = W / v, rs = stride == 1 ? 6 : 4;
+        const int rs = stride == 1 ? 6 : (p.OH <= 7 ? 7 : 4);
+        const int qw = W / v;
         const long long groups = (long long)p.planes * qw;
         const int strips = ceil_div(p.OH, rs);
         const long long warps = ceil_div<long long>(groups, 32) * strips;
         const long long blocks = ceil_div<long long>(warps, THREADS / 32);
         if(blocks > 0x7fffffffLL) return fail(DLP_INVALID_ARGUMENT, "depthwise problem too large for one launch");
-        if(stride == 1 && v == 4) depthwise3_reg_kernel<1, 4><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips);
-        else if(stride == 1) depthwise3_reg_kernel<1, 2><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips);
-        else if(v == 4) depthwise3_reg_kernel<2, 4><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips);
-        else depthwise3_reg_kernel<2, 2><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips);
+#define DLP_DW_REG(S, V, RS) depthwise3_reg_kernel<S, V, RS><<<(unsigned)blocks, THREADS, 0, stream>>>(p, groups, qw, strips)
+        switch(stride * 1000 + v * 100 + rs) {
+        case 1406: DLP_DW_REG(1, 4, 6); break;
+        case 1206: DLP_DW_REG(1, 2, 6); break;
+        case 2404: DLP_DW_REG(2, 4, 4); break;
+        case 2407: DLP_DW_REG(2, 4, 7); break;
+        case 2204: DLP_DW_REG(2, 2, 4); break;
+        default: DLP_DW_REG(2, 2, 7); break;
+        }
+#undef DLP_DW_REG
         DLP_LAUNCH_OK("depthwise3_reg_kernel");
         return DLP_OK;
     }

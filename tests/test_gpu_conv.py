@@ -440,11 +440,13 @@ def test_row_taps_loader(case):
 
 
 @pytest.mark.parametrize("case", [(2, 5, 9, 12, 1), (3, 7, 15, 14, 2), (1, 3, 6, 8, 2), (2, 4, 5, 6, 1), (1, 33, 7, 10, 2), (2, 40, 20, 36, 1),
-                                  (1, 6, 7, 7, 1)],
+                                  (1, 6, 7, 7, 1), (2, 8, 14, 14, 1), (1, 4, 12, 12, 1), (2, 5, 14, 14, 2), (1, 3, 13, 9, 1), (2, 9, 30, 11, 1),
+                                  (1, 5, 9, 7, 2)],
                          ids=lambda c: "x".join(str(v) for v in c))
 def test_depthwise_3x3_register_kernel(case):
     """Depthwise 3x3 / pad 1 at stride 1 and 2 over even widths (16- and 8-byte loads, halo by shuffle), odd heights, lane
-    counts that do not fill the last warp, bias + ReLU6, and y = factor*y + ...; the odd width takes the staged kernel."""
+    counts that do not fill the last warp, stride-2 planes that are one strip, bias + ReLU6, and y = factor*y + ...; the odd
+    widths take the staged kernel."""
     from dlprimitives_b200 import capi
     from oracle import bindings as ob
     N, C, H, W, stride = case
