@@ -70,6 +70,7 @@ struct Shared {
     unsigned long long acc_full[2];            // a chunk's partial sum is complete in tensor memory
     unsigned long long acc_empty[2];           // ... and has been read out (4 accumulate warps)
     unsigned long long drain;
+    unsigned long long sums_ready;             // the accumulate warps have reached the last chunk of the CTA's last work item
     uint32_t tmem_base;
     int abort_flag;
     uint32_t tma_issued;     // k-blocks whose bulk copies were issued
@@ -174,6 +175,7 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             mbar_init(&sh->acc_empty[a], NUM_ACC_WARPS * acc_sets);
         }
         mbar_init(&sh->drain, 1);
+        mbar_init(&sh->sums_ready, NUM_ACC_WARPS);
         sh->abort_flag = 0;
         sh->tma_issued = 0;
         sh->mma_consumed = 0;
@@ -190,6 +192,114 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *(volatile uint32_t *)&sh->tmem_base;
+
+    // ---- epilogue pieces shared by the accumulate warps and, for a CTA's last work item, the loader warps
+    // identity / relu / relu6 are a clamp; with no per-row bias and no beta the whole epilogue is
+    // add, clamp, (residual, clamp,) store.  Anything else takes the general path.
+    const float2 clamp = act_clamp(p.act), post_clamp = act_clamp(p.post_act);
+    const bool epi_fast = act_is_clamp(p.act) && act_is_clamp(p.post_act) && p.bias_mode != DLP_GEMM_BIAS_M && p.beta == 0.0f;
+    // The tile is handled 32 columns at a time: two tensor-memory loads under one wait; on the last
+    // chunk the residual operand of the same columns is fetched under that wait as well.
+    constexpr int G = BN >= 32 ? 32 : 16;
+    constexpr int GROUPS = BN / G;
+    const int chunks_per_tile = (kblocks + CHUNK_KB - 1) / CHUNK_KB;
+    const long long my_items = blockIdx.x < num_tiles ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // The epilogue of a CTA's last work item has nothing to hide behind.  When that tile is a whole one on the lean path,
+    // the loader warps (idle by then) take column groups of its last chunk: group 0 stays with the accumulate warps, 1 and 3
+    // go to the first loader group, 2 to the second.  Every side derives the decision from the same CTA-wide values.
+    const long long last_item = blockIdx.x + (my_items - 1) * gridDim.x;
+    bool tail_help = false;
+    if(my_items > 0 && !short_k && GROUPS >= 2 && epi_fast && !TC_DIAG(DIAG_NO_STORES)) {
+        long long t;
+        int part_unused;
+        decode_item(last_item, splits, t, part_unused);
+        tail_help = int(t % n_tiles) * BN + BN <= p.cols;
+    }
+    auto tail_owner = [](int g) { return g == 0 ? 0 : (g == 2 ? 2 : 1); };   // 0: accumulate warps, 1 / 2: loader groups
+    struct EpiItem {
+        RowInfo r;
+        long long row, col_stride;
+        int n0, part;
+        bool fast, with_res;
+        float *y_row;
+        const float *res_row;
+    };
+    auto epi_item = [&](long long item, int row_in_tile) {
+        EpiItem e;
+        long long tile;
+        decode_item(item, splits, tile, e.part);
+        e.n0 = int(tile % n_tiles) * BN;
+        e.row = (tile / n_tiles) * BM + row_in_tile;
+        e.r = make_row(p, e.row, a_off, y_off);
+        e.col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : (p.out_mode == OUT_COL_MAJOR ? p.ldc : 1ll);
+        e.fast = epi_fast && e.r.valid && e.n0 + BN <= p.cols && !TC_DIAG(DIAG_NO_STORES);
+        e.with_res = e.fast && p.residual != nullptr;
+        e.y_row = p.y + e.part * split_stride + e.r.out + (long long)e.n0 * e.col_stride;
+        e.res_row = e.with_res ? p.residual + e.r.out + (long long)e.n0 * e.col_stride : nullptr;
+        return e;
+    };
+    // Columns [g*G, g*G+G) of one chunk for the calling thread's row.  release_buf >= 0: after the tensor-memory read the
+    // warp hands that partial accumulator back to the MMA issuer.
+    auto epi_group = [&](const EpiItem &e, int g, uint32_t taddr, float *my_sums, bool first, bool last, int release_buf, int lane,
+                         uint32_t trace_idx) {
+        uint32_t v[G];
+        float res[G];
+        __syncwarp();
+        if(warp == WARP_ACC0 && lane == 0) TC_TRACE(9, trace_idx);
+        tmem_ld(taddr + g * G, v);
+        if(last && e.with_res) {
+            // the residual operand of these columns travels while the tensor-memory load does
+            const float *rp = e.res_row + (long long)(g * G) * e.col_stride;
+            #pragma unroll
+            for(int j = 0; j < G; j++) { res[j] = TC_DIAG(DIAG_NO_RESIDUAL_LOADS) ? 0.5f : __ldg(rp); rp += e.col_stride; }
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if(warp == WARP_ACC0 && lane == 0) TC_TRACE(10, trace_idx);
+        if(release_buf >= 0) {
+            // the partial accumulator is fully read: hand it back to the MMA issuer
+            tc_fence_before();
+            __syncwarp();
+            if(lane == 0) mbar_arrive(&sh->acc_empty[release_buf]);
+        }
+        float x[G];
+        float *sg = my_sums + g * G * BM;
+        #pragma unroll
+        for(int j = 0; j < G; j++) x[j] = first ? __uint_as_float(v[j]) : sg[j * BM] + __uint_as_float(v[j]);
+        if(!last) {
+            #pragma unroll
+            for(int j = 0; j < G; j++) sg[j * BM] = x[j];
+            return;
+        }
+        // ---- last chunk: these columns of the row are final
+        const int col0 = e.n0 + g * G;
+        if(e.fast) {
+            float *y0 = e.y_row + (long long)(g * G) * e.col_stride;
+            const float *b0 = p.bias + col0;
+            const bool nb = TC_DIAG(DIAG_NO_BIAS_LOADS), ns = TC_DIAG(DIAG_LEAN_NO_STG);
+            if(e.with_res) {
+                if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, true>(x, y0, res, e.col_stride, b0, clamp, p.residual_scale, post_clamp, nb, ns);
+                else store_cols<G, false, true>(x, y0, res, e.col_stride, b0, clamp, p.residual_scale, post_clamp, nb, ns);
+            }
+            else {
+                if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, false>(x, y0, res, e.col_stride, b0, clamp, 0.0f, post_clamp, nb, ns);
+                else store_cols<G, false, false>(x, y0, res, e.col_stride, b0, clamp, 0.0f, post_clamp, nb, ns);
+            }
+        }
+        else {
+            // general epilogue: the values pass through the thread's own slots of the sums tile so
+            // that this loop can index them (a register array indexed by a loop counter would live
+            // in local memory on every path)
+            #pragma unroll
+            for(int j = 0; j < G; j++) sg[j * BM] = x[j];
+            if(e.r.valid && !TC_DIAG(DIAG_NO_STORES)) {
+                #pragma unroll 1
+                for(int j = 0; j < G; j++)
+                    if(col0 + j < p.cols)
+                        p.y[e.part * split_stride + out_index(p, e.r, col0 + j)] = finish_output(p, e.r, e.row, col0 + j, sg[j * BM]);
+            }
+        }
+        if(warp == WARP_ACC0 && lane == 0) TC_TRACE(11, trace_idx);
+    };
 
     if(warp == WARP_TMA) {
         // ------------------------------------------------------------------ B producer
@@ -361,35 +471,26 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
         const int acc_set = warp < WARP_LOAD0 ? 0 : 1;      // which of the acc_sets sets of epilogue warps this one is in
         const int row_in_tile = quad * 32 + lane;
         float *my_sums = sums + row_in_tile;                // element (col) at my_sums[col * BM]: conflict-free
-        const int chunks_per_tile = (kblocks + CHUNK_KB - 1) / CHUNK_KB;
         uint32_t chunk = 0, items_begun = 0;
-        // identity / relu / relu6 are a clamp; with no per-row bias and no beta the whole epilogue is
-        // add, clamp, (residual, clamp,) store.  Anything else takes the general path.
-        const float2 clamp = act_clamp(p.act), post_clamp = act_clamp(p.post_act);
-        const bool epi_fast = act_is_clamp(p.act) && act_is_clamp(p.post_act) && p.bias_mode != DLP_GEMM_BIAS_M && p.beta == 0.0f;
         bool live = true;
         for(long long item = blockIdx.x; item < num_tiles && live; item += gridDim.x) {
-            long long tile;
-            int part;
-            decode_item(item, splits, tile, part);
-            const int n0 = int(tile % n_tiles) * BN;
-            const long long row = (tile / n_tiles) * BM + row_in_tile;
-            const RowInfo r = make_row(p, row, a_off, y_off);
-            const long long col_stride = p.out_mode == OUT_NCHW ? (long long)p.plane : (p.out_mode == OUT_COL_MAJOR ? p.ldc : 1ll);
-            // The tile is handled 32 columns at a time: two tensor-memory loads under one wait; on the last
-            // chunk the residual operand of the same columns is fetched under that wait as well.
-            constexpr int G = BN >= 32 ? 32 : 16;
-            constexpr int GROUPS = BN / G;
-            const bool fast = epi_fast && r.valid && n0 + BN <= p.cols && !TC_DIAG(DIAG_NO_STORES);
-            const bool with_res = fast && p.residual != nullptr;
-            float *y_row = p.y + part * split_stride + r.out + (long long)n0 * col_stride;
-            const float *res_row = with_res ? p.residual + r.out + (long long)n0 * col_stride : nullptr;
+            const EpiItem e = epi_item(item, row_in_tile);
+            const RowInfo &r = e.r;
+            const int n0 = e.n0, part = e.part;
+            const long long row = e.row, col_stride = e.col_stride;
+            float *y_row = e.y_row;
             // A tile whose last columns lie beyond the matrix takes its own, rolled path: groups of columns that do
             // not exist are skipped and the others go column by column through the lean arithmetic when it applies.
             const bool ragged_tile = n0 + BN > p.cols;
             for(int c = 0; c < chunks_per_tile; c++, chunk++) {
                 const uint32_t buf = chunk & 1;
                 const bool first = c == 0, last = c == chunks_per_tile - 1;
+                // the last chunk of the CTA's last item is shared with the loader warps: every earlier sum of the tile is in place
+                const bool shared_tail = tail_help && last && item == last_item;
+                if(shared_tail) {
+                    __syncwarp();
+                    if(lane == 0) mbar_arrive(&sh->sums_ready);
+                }
                 if(!warp_wait(&sh->acc_full[buf], (chunk >> 1) & 1, &sh->abort_flag, status, ST_EPI_ACC, lane)) { live = false; break; }
                 if(c == 0 && warp == WARP_ACC0 && lane == 0) *(volatile uint32_t *)&sh->epilogue_started = ++items_begun;
                 tc_fence_after();
@@ -438,61 +539,8 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
                 }
                 #pragma unroll 1
                 for(int g = acc_set; g < GROUPS; g += acc_sets) {
-                    uint32_t v[G];
-                    float res[G];
-                    __syncwarp();
-                    if(warp == WARP_ACC0 && lane == 0) TC_TRACE(9, chunk * GROUPS + g);
-                    tmem_ld(taddr + g * G, v);
-                    if(last && with_res) {
-                        // the residual operand of these columns travels while the tensor-memory load does
-                        const float *rp = res_row + (long long)(g * G) * col_stride;
-                        #pragma unroll
-                        for(int j = 0; j < G; j++) { res[j] = TC_DIAG(DIAG_NO_RESIDUAL_LOADS) ? 0.5f : __ldg(rp); rp += col_stride; }
-                    }
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if(warp == WARP_ACC0 && lane == 0) TC_TRACE(10, chunk * GROUPS + g);
-                    if(g + acc_sets >= GROUPS) {
-                        // the partial accumulator is fully read: hand it back to the MMA issuer
-                        tc_fence_before();
-                        __syncwarp();
-                        if(lane == 0) mbar_arrive(&sh->acc_empty[buf]);
-                    }
-                    float x[G];
-                    float *sg = my_sums + g * G * BM;
-                    #pragma unroll
-                    for(int j = 0; j < G; j++) x[j] = first ? __uint_as_float(v[j]) : sg[j * BM] + __uint_as_float(v[j]);
-                    if(!last) {
-                        #pragma unroll
-                        for(int j = 0; j < G; j++) sg[j * BM] = x[j];
-                        continue;
-                    }
-                    // ---- last chunk: these columns of the row are final
-                    const int col0 = n0 + g * G;
-                    if(fast) {
-                        float *y0 = y_row + (long long)(g * G) * col_stride;
-                        const float *b0 = p.bias + col0;
-                        if(with_res) {
-                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp, TC_DIAG(DIAG_NO_BIAS_LOADS), TC_DIAG(DIAG_LEAN_NO_STG));
-                            else store_cols<G, false, true>(x, y0, res, col_stride, b0, clamp, p.residual_scale, post_clamp, TC_DIAG(DIAG_NO_BIAS_LOADS), TC_DIAG(DIAG_LEAN_NO_STG));
-                        }
-                        else {
-                            if(p.bias_mode == DLP_GEMM_BIAS_N) store_cols<G, true, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp, TC_DIAG(DIAG_NO_BIAS_LOADS), TC_DIAG(DIAG_LEAN_NO_STG));
-                            else store_cols<G, false, false>(x, y0, res, col_stride, b0, clamp, 0.0f, post_clamp, TC_DIAG(DIAG_NO_BIAS_LOADS), TC_DIAG(DIAG_LEAN_NO_STG));
-                        }
-                    }
-                    else {
-                        // general epilogue: the values pass through the thread's own slots of the sums tile so
-                        // that this loop can index them (a register array indexed by a loop counter would live
-                        // in local memory on every path)
-                        #pragma unroll
-                        for(int j = 0; j < G; j++) sg[j * BM] = x[j];
-                        if(r.valid && !TC_DIAG(DIAG_NO_STORES)) {
-                            #pragma unroll 1
-                            for(int j = 0; j < G; j++)
-                                if(col0 + j < p.cols) p.y[part * split_stride + out_index(p, r, col0 + j)] = finish_output(p, r, row, col0 + j, sg[j * BM]);
-                        }
-                    }
-                    if(warp == WARP_ACC0 && lane == 0) TC_TRACE(11, chunk * GROUPS + g);
+                    if(shared_tail && tail_owner(g) != 0) continue;       // a loader group's columns (nobody waits for this buffer again)
+                    epi_group(e, g, taddr, my_sums, first, last, g + acc_sets >= GROUPS ? int(buf) : -1, lane, chunk * GROUPS + g);
                 }
             }
         }
@@ -669,6 +717,19 @@ contraction_tf32x3_kernel(const float *__restrict__ packed, const Contraction p,
             cur = nxt;
             have_cur = true;
             advance(nxt, groups);
+        }
+        // ---- the last chunk of the CTA's last work item: this loader group's share of the epilogue
+        if(tail_help && !*(volatile int *)&sh->abort_flag) {
+            const uint32_t last_chunk = uint32_t(my_items * chunks_per_tile - 1), buf = last_chunk & 1;
+            if(warp_wait(&sh->sums_ready, 0, &sh->abort_flag, status, ST_EPI_ACC, lane) &&
+               warp_wait(&sh->acc_full[buf], (last_chunk >> 1) & 1, &sh->abort_flag, status, ST_EPI_ACC, lane)) {
+                tc_fence_after();
+                const EpiItem e = epi_item(last_item, row_in_tile);
+                const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + buf * BN;
+                #pragma unroll 1
+                for(int g = 1; g < GROUPS; g++)
+                    if(tail_owner(g) == group + 1) epi_group(e, g, taddr, sums + row_in_tile, chunks_per_tile == 1, true, -1, lane, 0);
+            }
         }
     }
 
