@@ -312,7 +312,7 @@ dlp_status dlp_pooling2d_fwd(const float *x, float *y, int planes, int in_h, int
     if(total <= 0) return DLP_OK;
     if(mode == 0 && kernel[0] == 3 && kernel[1] == 3 && stride[0] == 2 && stride[1] == 2 && pad[0] == 1 && pad[1] == 1 && in_w % 2 == 0 &&
        2 * ow <= in_w && reinterpret_cast<uintptr_t>(x) % 8 == 0) {
-        constexpr int RS = 8;
+        constexpr int RS = 4;      // 4-row strips: measured faster than 8 (fewer registers, more warps in flight)
         const int col_blocks = ceil_div(ow, 32), strips = ceil_div(oh, RS);
         const long long items = (long long)planes * col_blocks * strips;
         pool_max3s2_kernel<RS><<<unsigned(ceil_div<long long>(items, 8)), 256, 0, (cudaStream_t)stream>>>(x, y, items, col_blocks, strips, in_h, in_w,
