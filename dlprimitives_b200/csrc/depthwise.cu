@@ -257,6 +257,61 @@ __global__ void __launch_bounds__(THREADS) depthwise3_reg_kernel(DwParams p, lon
     }
 }
 
+
+// 1x1 depthwise (one weight per channel): y = act(w[c] * x + b[c]) [+ factor * y], element by element.  A thread takes four
+// consecutive elements (one 16-byte access each way when the plane size is a multiple of 4 and the tensors are aligned),
+// U such groups a grid stride apart with their loads issued together; the plane index is a 32-bit division.
+__global__ void __launch_bounds__(THREADS) depthwise1_scale_kernel(DwParams p, unsigned total4, unsigned total, int plane, int vec)
+{
+    constexpr int U = 4;
+    const unsigned nthreads = gridDim.x * blockDim.x;
+    for(unsigned g0 = blockIdx.x * blockDim.x + threadIdx.x; g0 < total4; g0 += U * nthreads) {
+        float v[U][4];
+        #pragma unroll
+        for(int u = 0; u < U; u++) {
+            const unsigned g = g0 + u * nthreads;
+            if(g >= total4) continue;
+            if(vec) {
+                const float4 t = __ldg(reinterpret_cast<const float4 *>(p.x) + g);
+                v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
+            }
+            else
+                for(int j = 0; j < 4; j++) v[u][j] = 4 * g + j < total ? __ldg(p.x + 4 * g + j) : 0.0f;
+        }
+        #pragma unroll
+        for(int u = 0; u < U; u++) {
+            const unsigned g = g0 + u * nthreads;
+            if(g >= total4) continue;
+            float o[4];
+            // vec: the four elements lie in one plane and share its weight and bias
+            unsigned c = ((4 * g) / unsigned(plane)) % unsigned(p.channels);
+            float wc = __ldg(p.w + c), bc = p.bias ? __ldg(p.bias + c) : 0.0f;
+            #pragma unroll
+            for(int j = 0; j < 4; j++) {
+                if(!vec && j > 0) {
+                    c = ((4 * g + j) / unsigned(plane)) % unsigned(p.channels);
+                    wc = __ldg(p.w + c);
+                    bc = p.bias ? __ldg(p.bias + c) : 0.0f;
+                }
+                float a = fmaf(v[u][j], wc, 0.0f);
+                if(p.bias) a += bc;
+                o[j] = apply_act(a, p.act);
+            }
+            if(vec) {
+                float4 *dst = reinterpret_cast<float4 *>(p.y) + g;
+                if(p.factor != 0.0f) {
+                    const float4 t = *dst;
+                    o[0] += p.factor * t.x; o[1] += p.factor * t.y; o[2] += p.factor * t.z; o[3] += p.factor * t.w;
+                }
+                *dst = make_float4(o[0], o[1], o[2], o[3]);
+            }
+            else
+                for(int j = 0; j < 4; j++)
+                    if(4 * g + j < total) p.y[4 * g + j] = p.factor != 0.0f ? o[j] + p.factor * p.y[4 * g + j] : o[j];
+        }
+    }
+}
+
 } // namespace
 
 bool depthwise_supported(int ks_h, int ks_w, int stride_h, int stride_w, int pad_h, int pad_w, int dil_h, int dil_w, int in_w)
@@ -280,6 +335,15 @@ dlp_status launch_depthwise(const float *x, const float *w, const float *bias, f
     p.planes = batch * channels;
     p.act = act; p.factor = factor;
     if(p.planes <= 0 || p.OH <= 0 || p.OW <= 0) return DLP_OK;
+    if(ks == 1 && stride == 1 && pad == 0 && (long long)p.planes * H * W < (1ll << 32) - 4) {
+        const unsigned total = unsigned((long long)p.planes * H * W), total4 = (total + 3) / 4;
+        const int plane = H * W;
+        const int vec = plane % 4 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
+        const unsigned blocks = std::max(1u, std::min(ceil_div(total4, unsigned(THREADS * 4)), unsigned(16 * sm_count())));
+        depthwise1_scale_kernel<<<blocks, THREADS, 0, stream>>>(p, total4, total, plane, vec);
+        DLP_LAUNCH_OK("depthwise1_scale_kernel");
+        return DLP_OK;
+    }
     // (measured on the MobileNetV2 rows: odd widths -- 4-byte loads -- and whole 14-row planes as one strip at stride 1
     // are no faster than the staged kernel or the 6-row strips, so those variants are not kept)
     if(ks == 3 && pad == 1 && W % 2 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {

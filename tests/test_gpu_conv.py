@@ -465,3 +465,23 @@ def test_depthwise_3x3_register_kernel(case):
         got = y.cpu().numpy()
         assert got.shape == want.shape
         assert rel_err(got, want + factor * y0) <= REL_TOL, (case, factor)
+
+
+@pytest.mark.parametrize("shape", [(2, 6, 8, 8), (1, 5, 7, 7), (3, 16, 13, 4), (1, 2, 1, 3)], ids=lambda c: "x".join(str(v) for v in c))
+def test_depthwise_1x1_scale(shape):
+    """A 1x1 depthwise convolution is a per-channel scale: planes of a multiple of 4 elements (16-byte path) and not,
+    bias + ReLU6, y = factor*y + ..."""
+    from dlprimitives_b200 import capi
+    from oracle import bindings as ob
+    N, C, H, W = shape
+    rng = np.random.default_rng(N + 10 * C + H)
+    x = rng.standard_normal(shape, dtype=np.float32) * 3
+    w = rng.standard_normal((C, 1, 1, 1), dtype=np.float32)
+    b = rng.uniform(-0.5, 0.5, C).astype(np.float32)
+    plan = capi.Conv2DForward(channels_in=C, channels_out=C, kernel=1, groups=C, batch=N, height=H, width=W, bias=True, activation="relu6")
+    want = ob.conv2d(x, w, b, groups=C, activation="relu6")
+    y0 = rng.standard_normal(want.shape).astype(np.float32)
+    for factor in (0.0, -1.5):
+        y = to_dev(y0) if factor else torch.full(plan.output_shape(N), float("nan"), device=DEV)
+        plan.enqueue(to_dev(x), to_dev(w), to_dev(b), y, None, factor=factor)
+        assert rel_err(y.cpu().numpy(), want + factor * y0) <= 1e-6, (plan.algo(), plan.kernel(), factor)
