@@ -296,7 +296,8 @@ def run_gpu_arm(args, rank, world, local_rank):
     net_json = resnet50.make_json(local_batch)
     params = resnet50.make_params(net_json, seed=0)           # every rank holds the full weights
     x_all = resnet50.make_input(resnet50.make_json(GLOBAL_BATCH), seed=1)
-    net = hostapi.Net(net_json, device=local_rank)
+    # the projection shortcuts of the four stage-opening blocks run on a second stream (a Net option, bit-identical results)
+    net = hostapi.Net(net_json, device=local_rank, flags=hostapi.Net.CONCURRENT_BRANCHES)
     for name, value in params.items():
         net.set_param(name, value)
     net.upload_params()

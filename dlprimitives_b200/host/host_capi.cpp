@@ -126,6 +126,7 @@ int dlp_net_create(const char *net_json, int device, int flags, dlp_net **out)
     h->net.keep_intermediate_tensors((flags & 1) != 0);
     h->net.fuse_operators((flags & 2) == 0);
     h->net.use_cuda_graph((flags & 4) == 0);
+    h->net.concurrent_branches((flags & 16) != 0);
     json::value description = json::parse(net_json);
     if(flags & 8) Net::merge_activations(description);
     h->net.load_from_json(description);

@@ -17,7 +17,12 @@ namespace dlprim {
 using host::cuda_check;
 
 Net::Net(Context &ctx) : ctx_(ctx) {}
-Net::~Net() { drop_graph(); }
+Net::~Net()
+{
+    drop_graph();
+    for(cudaEvent_t ev : side_events_) cudaEventDestroy(ev);
+    if(side_stream_) cudaStreamDestroy(side_stream_);
+}
 
 void Net::mode(CalculationsMode m)
 {
@@ -276,6 +281,47 @@ void Net::build_plan()
         }
         steps_.push_back(st);
     }
+
+    // Concurrent branches: a plain convolution whose inputs were complete well before its turn (nothing between their last
+    // writer and the convolution writes them or touches its output's storage) is launched on the second stream as soon
+    // as those inputs are ready and joined before the first step that touches its result.
+    if(side_branches_ && !keep_intermediate_tensors_) {
+        auto roots = [&](std::vector<std::string> const &names) {
+            std::set<std::string> r;
+            for(std::string const &n : names) r.insert(root_of(n));
+            return r;
+        };
+        auto touches = [&](Step const &st, std::set<std::string> const &rs, bool reads_too) {
+            for(std::string const &n : st.writes) if(rs.count(root_of(n))) return true;
+            if(reads_too) for(std::string const &n : st.reads) if(rs.count(root_of(n))) return true;
+            return false;
+        };
+        int busy_until = -1;                       // one branch at a time on the second stream
+        for(int s = 0; s < int(steps_.size()); s++) {
+            Step &st = steps_[s];
+            if(st.kind != Step::plain || !dynamic_cast<Convolution2D *>(connections_[st.conn].op.get())) continue;
+            const std::set<std::string> in = roots(st.reads), out = roots(st.writes);
+            bool overlap = false;
+            for(std::string const &r : in) overlap = overlap || out.count(r);
+            if(overlap) continue;
+            int w = -1;                             // last step before s that writes an input
+            for(int m = s - 1; m >= 0 && w < 0; m--) if(touches(steps_[m], in, false)) w = m;
+            if(w >= s - 1 || w + 1 <= busy_until) continue;
+            bool ok = true;
+            for(int m = w + 1; m < s && ok; m++) ok = !touches(steps_[m], out, true);
+            int j = -1;                             // first step after s that touches the result
+            for(int m = s + 1; m < int(steps_.size()) && j < 0; m++) {
+                if(touches(steps_[m], out, true)) j = m;
+                else if(touches(steps_[m], in, false)) ok = false;      // an input rewritten while the branch may still read it
+            }
+            if(!ok || j < 0) continue;
+            for(std::string const &o : outputs_) ok = ok && !out.count(root_of(o));
+            if(!ok) continue;
+            st.fork_at = w + 1;
+            st.join_at = j;
+            busy_until = j;
+        }
+    }
 }
 
 // -------------------------------------------------------------------------------------------- memory
@@ -292,6 +338,12 @@ void Net::allocate_tensors()
     };
     for(std::string const &in : inputs_) touch(in, -1);
     for(int s = 0; s < int(steps_.size()); s++) {
+        // a step on the second stream may write its result from its launch point on and read its inputs until it is joined
+        for(Step const &side : steps_)
+            if(side.fork_at == s) {
+                for(std::string const &n : side.writes) { touch(n, s); touch(n, side.join_at); }
+                for(std::string const &n : side.reads) touch(n, side.join_at);
+            }
         for(std::string const &n : steps_[s].writes) touch(n, s);
         for(std::string const &n : steps_[s].reads) touch(n, s);
     }
@@ -381,6 +433,9 @@ void Net::bind_tensors()
         for(std::string const &n : c.parameter_names) c.parameters.push_back(parameters_.at(n));
     }
     workspace_ = ws > 0 ? Tensor(ctx_, Shape(ws), uint8_data) : Tensor();
+    size_t side_ws = 0;
+    for(Step const &st : steps_) if(st.fork_at >= 0) side_ws = std::max(side_ws, connections_[st.conn].ws_size);
+    side_workspace_ = side_ws > 0 ? Tensor(ctx_, Shape(side_ws), uint8_data) : Tensor();
 }
 
 void Net::setup()
@@ -542,16 +597,50 @@ Tensor &Net::output(unsigned id)
 // -------------------------------------------------------------------------------------------- forward
 void Net::run_steps(ExecutionContext const &e)
 {
-    for(Step const &st : steps_) {
+    auto run = [&](Step const &st, ExecutionContext const &ex, Tensor &ws) {
         Connection &c = connections_[st.conn];
-        ExecGuard g(e, c.name.c_str());
+        ExecGuard g(ex, c.name.c_str());
         if(st.kind == Step::conv_residual) {
             Convolution2D *conv = static_cast<Convolution2D *>(c.op.get());
-            conv->forward_fused(c.input_tensors[0], tensors_.at(st.result), c.parameters, workspace_, tensors_.at(st.residual),
-                                st.residual_scale, st.post_activation, e);
+            conv->forward_fused(c.input_tensors[0], tensors_.at(st.result), c.parameters, ws, tensors_.at(st.residual),
+                                st.residual_scale, st.post_activation, ex);
         }
         else
-            c.op->forward(c.input_tensors, c.output_tensors, c.parameters, workspace_, e);
+            c.op->forward(c.input_tensors, c.output_tensors, c.parameters, ws, ex);
+    };
+    // the second stream is used with a real stream and without per-operator timing (which wants one stream's order)
+    bool side = e.stream() != nullptr && !e.timing_enabled();
+    if(side) {
+        size_t wanted = 0;
+        for(Step const &st : steps_) if(st.fork_at >= 0) wanted += 2;
+        side = wanted > 0;
+        if(side && !side_stream_) cuda_check(cudaStreamCreateWithFlags(&side_stream_, cudaStreamNonBlocking), "cudaStreamCreateWithFlags");
+        while(side && side_events_.size() < wanted) {
+            cudaEvent_t ev;
+            cuda_check(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "cudaEventCreateWithFlags");
+            side_events_.push_back(ev);
+        }
+    }
+    ExecutionContext side_e(side_stream_);
+    for(int k = 0; k < int(steps_.size()); k++) {
+        if(side) {
+            size_t ev = 0;
+            for(Step const &br : steps_) {
+                if(br.fork_at < 0) continue;
+                if(br.fork_at == k) {
+                    // the branch starts when everything before step k is done, on its own stream and workspace
+                    cuda_check(cudaEventRecord(side_events_[ev], e.stream()), "cudaEventRecord");
+                    cuda_check(cudaStreamWaitEvent(side_stream_, side_events_[ev], 0), "cudaStreamWaitEvent");
+                    run(br, side_e, side_workspace_);
+                    cuda_check(cudaEventRecord(side_events_[ev + 1], side_stream_), "cudaEventRecord");
+                }
+                if(br.join_at == k) cuda_check(cudaStreamWaitEvent(e.stream(), side_events_[ev + 1], 0), "cudaStreamWaitEvent");
+                ev += 2;
+            }
+        }
+        Step const &st = steps_[k];
+        if(side && st.fork_at >= 0) continue;        // ran on the second stream
+        run(st, e, workspace_);
     }
 }
 
@@ -611,6 +700,9 @@ std::vector<std::string> Net::describe_plan() const
             line += std::string(" ") + ip->kernel_name();
         if(st.kind == Step::conv_residual)
             line += " +residual(" + st.residual + ")->" + st.result + " absorbs " + connections_[st.fused_conn].name;
+        if(st.fork_at >= 0)
+            line += " [second stream: from before " + connections_[steps_[st.fork_at].conn].name + " until " +
+                    connections_[steps_[st.join_at].conn].name + "]";
         lines.push_back(line);
     }
     return lines;

@@ -141,7 +141,7 @@ class Operator:
 
 class Net:
     """A dlprim::Net built from the network JSON (predict mode, setup done)."""
-    KEEP_INTERMEDIATE, NO_FUSION, NO_GRAPH = 1, 2, 4
+    KEEP_INTERMEDIATE, NO_FUSION, NO_GRAPH, MERGE_ACTIVATIONS, CONCURRENT_BRANCHES = 1, 2, 4, 8, 16
 
     def __init__(self, net_json, device=0, flags=0):
         text = net_json if isinstance(net_json, str) else json.dumps(net_json)

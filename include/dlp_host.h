@@ -43,7 +43,7 @@ DLP_HOST_API int dlp_op_forward(dlp_op *op, void *const *device_inputs, void *co
 /* ---- a whole network (include/dlprim/net.hpp) ---- */
 typedef struct dlp_net dlp_net;
 /* flags: bit 0 keep intermediate tensors, bit 1 no operator fusion, bit 2 no CUDA graph, bit 3 run Net::merge_activations on
- * the description first */
+ * the description first, bit 4 concurrent branches (Net::concurrent_branches: projection shortcuts on a second stream) */
 DLP_HOST_API int dlp_net_create(const char *net_json, int device, int flags, dlp_net **out);
 DLP_HOST_API void dlp_net_destroy(dlp_net *net);
 DLP_HOST_API int dlp_net_num_params(const dlp_net *net);

@@ -50,6 +50,11 @@ public:
     void fuse_operators(bool v) { fuse_ = v; }
     /// Replay forward() as a CUDA graph from the second call on (default on).
     void use_cuda_graph(bool v) { use_graph_ = v; drop_graph(); }
+    /// Run a convolution that does not depend on the operators just before it (the projection shortcut of a residual
+    /// block) on a second stream, from the point where its inputs are ready to the point where its result is first used.
+    /// Takes effect at the next setup().  Default off.
+    void concurrent_branches(bool v) { side_branches_ = v; }
+    bool concurrent_branches() const { return side_branches_; }
 
     /// Allocate tensors, parameters and the workspace; build the execution plan.
     void setup();
@@ -101,6 +106,8 @@ private:
         float residual_scale = 1.0f;
         StandardActivations post_activation = StandardActivations::identity;
         std::vector<std::string> reads, writes;
+        // concurrent branches: this step runs on the second stream, launched before step fork_at and joined before step join_at
+        int fork_at = -1, join_at = -1;
     };
     void build_plan();
     void allocate_tensors();
@@ -114,6 +121,7 @@ private:
     CalculationsMode mode_ = CalculationsMode::predict;
     bool keep_intermediate_tensors_ = false;
     bool fuse_ = true, use_graph_ = true;
+    bool side_branches_ = false;
     bool is_setup_ = false;
 
     std::map<std::string, TensorSpecs> tensor_specs_;
@@ -125,6 +133,7 @@ private:
     std::vector<std::string> inputs_, outputs_;
 
     Tensor workspace_;
+    Tensor side_workspace_;      // for the steps on the second stream
     Tensor pool_;
     std::map<std::string, Tensor> tensors_;
     std::map<std::string, Tensor> parameters_;
@@ -132,6 +141,8 @@ private:
 
     cudaGraphExec_t graph_exec_ = nullptr;
     cudaStream_t graph_stream_ = nullptr;
+    cudaStream_t side_stream_ = nullptr;
+    std::vector<cudaEvent_t> side_events_;   // two per step on the second stream: inputs ready, result ready
     int forwards_since_change_ = 0;
 };
 

@@ -46,7 +46,8 @@ def run_gpu(net, x, outputs=("fc", "prob"), repeats=3):
 
 
 @pytest.mark.parametrize("case", list(net_golden.CASES))
-@pytest.mark.parametrize("flags", [0, 2, 1 | 4], ids=["fused+graph", "unfused+graph", "keep_intermediate+eager"])
+@pytest.mark.parametrize("flags", [0, 2, 1 | 4, 16, 16 | 4], ids=["fused+graph", "unfused+graph", "keep_intermediate+eager", "branches+graph",
+                                                             "branches+eager"])
 def test_small_resnet_against_reference_cpu_outputs(case, flags):
     from dlprimitives_b200 import capi, resnet50
     batch, h, w, folded, div, pseed, iseed = net_golden.CASES[case]
@@ -57,7 +58,11 @@ def test_small_resnet_against_reference_cpu_outputs(case, flags):
     net = build_gpu_net(net_json, params, flags)
     plan = net.plan()
     fused = [line for line in plan if "+residual" in line]
-    if flags == 0 and folded:
+    if flags & 16:
+        # the four projection shortcuts run on the second stream, from the block's input to the convolution that adds them
+        side = [line for line in plan if "[second stream" in line]
+        assert len(side) == 4 and all(".downsample" in line.split()[0] for line in side), plan
+    if flags in (0, 16, 20) and folded:
         assert len(fused) == 16, plan             # every bottleneck's sum is folded into a convolution
         assert not any(" Elementwise" in line for line in plan)
     else:
@@ -278,3 +283,18 @@ def test_activation_merge_keeps_the_results():
     a = run_gpu(plain, x, outputs=("t11", "t15"), repeats=2)[-1]
     b = run_gpu(merged, x, outputs=("t11", "t15"), repeats=2)[-1]
     assert np.array_equal(a["t11"], b["t11"]) and np.array_equal(a["t15"], b["t15"])
+
+
+def test_concurrent_branches_give_the_same_bits():
+    """With the projection shortcuts on a second stream the same kernels run on the same data: the outputs are
+    bit-identical to the one-stream run, eager, captured and replayed, and the activation pool only grows."""
+    from dlprimitives_b200 import hostapi, resnet50
+    net_json = resnet50.make_json(6, 64, 64, folded=True, width_div=4)
+    params = resnet50.make_params(net_json, seed=3)
+    x = resnet50.make_input(net_json, seed=4)
+    one = build_gpu_net(net_json, params, 0)
+    two = build_gpu_net(net_json, params, hostapi.Net.CONCURRENT_BRANCHES)
+    a, b = run_gpu(one, x, repeats=4), run_gpu(two, x, repeats=4)
+    for ra, rb in zip(a, b):
+        assert np.array_equal(ra["fc"], rb["fc"]) and np.array_equal(ra["prob"], rb["prob"])
+    assert two.activation_bytes() >= one.activation_bytes()
