@@ -162,6 +162,12 @@ dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const 
 bool pointwise_tc_eligible(const Contraction &p, const TcPacked &L);
 dlp_status launch_pointwise_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream);
 
+// Convolutions with at most 64 output channels over rows of a multiple of four pixels (the 7x7 stem, 3x3 over 64 channels): the
+// input patch of a tile of whole output rows comes in by one tensor-map copy per channel block and every tap is gathered from
+// shared memory (staged_tc.cu).  launch_contraction_tc hands eligible problems over by itself.
+bool staged_tc_eligible(const Contraction &p, const TcPacked &L);
+dlp_status launch_staged_tc(const Contraction &p, const TcPacked &L, const float *packed, cudaStream_t stream);
+
 // Winograd F(2x2, 3x3), stride 1, padding 1 (winograd.cu).  u: the transformed filters, winograd_packed_bytes() long.
 size_t winograd_packed_bytes(int cin, int cout);
 dlp_status winograd_filter_transform(const float *w, float *u, int cin, int cout, cudaStream_t stream);

@@ -967,6 +967,8 @@ dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const 
     if(batch.count > 65535) return fail(DLP_INVALID_ARGUMENT, "a batched product takes at most 65535 matrices");
     int splits = batch.count > 1 ? 1 : choose_splits(p.rows, L);      // the matrices of a batch fill the GPU between them
     if(splits == 1 && batch.count == 1 && pointwise_tc_eligible(p, L)) return launch_pointwise_tc(p, L, packed, stream);
+    static const bool no_staged = getenv("DLP_TC_NO_STAGED") != nullptr;
+    if(splits == 1 && batch.count == 1 && !no_staged && staged_tc_eligible(p, L)) return launch_staged_tc(p, L, packed, stream);
     const long long rows_pad = ceil_div<long long>(p.rows, tc::BM) * tc::BM;
     const long long split_stride = rows_pad * L.n_pad;
     if(splits > 1 && (scratch == nullptr || scratch_bytes < size_t(splits) * split_stride * sizeof(float))) splits = 1;
