@@ -967,6 +967,7 @@ dlp_status launch_contraction_tc(const Contraction &p, const TcPacked &L, const 
     if(batch.count > 65535) return fail(DLP_INVALID_ARGUMENT, "a batched product takes at most 65535 matrices");
     int splits = batch.count > 1 ? 1 : choose_splits(p.rows, L);      // the matrices of a batch fill the GPU between them
     if(splits == 1 && batch.count == 1 && pointwise_tc_eligible(p, L)) return launch_pointwise_tc(p, L, packed, stream);
+    // (environment variable DLP_TC_NO_STAGED: keep such problems on this file's kernel, for A/B timing and profiling)
     static const bool no_staged = getenv("DLP_TC_NO_STAGED") != nullptr;
     if(splits == 1 && batch.count == 1 && !no_staged && staged_tc_eligible(p, L)) return launch_staged_tc(p, L, packed, stream);
     const long long rows_pad = ceil_div<long long>(p.rows, tc::BM) * tc::BM;
