@@ -329,6 +329,8 @@ staged_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
         long long i = 0;
         for(long long item = blockIdx.x; item < q.num_items && live; item += gridDim.x, i++) {
             const Item w = decode(item, q);
+            // the bias of the set's 32 channels is asked for now: its trip to L2 is over long before the last chunk is in
+            const float bias_lane = q.bias && w.n_tile * BN + g * 32 + lane < q.cols ? ldg_early(q.bias + w.n_tile * BN + g * 32 + lane) : 0.0f;
             float sum[32];
             bool ok = true;
             #pragma unroll 1
@@ -351,7 +353,6 @@ staged_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
             const int e = j % E_BUFS;
             const int col0 = w.n_tile * BN + g * 32;
             if(ok) {
-                const float bias_lane = q.bias && col0 + lane < q.cols ? __ldg(q.bias + col0 + lane) : 0.0f;
                 ok = warp_wait(&sh->e_empty[e], ((j / E_BUFS) & 1) ^ 1, abort_flag, status, ST_EPI_BUF, lane);
                 if(ok) {
                     float *slot = e_bufs + e * (E_BUF_BYTES / 4);      // [channel of the group][valid pixels]

@@ -90,6 +90,22 @@ __device__ __forceinline__ bool warp_wait(unsigned long long *bar, uint32_t pari
     __syncwarp();
     return ok != 0;
 }
+// For a converged warp that expects the barrier to be complete already: every lane tries it (one uniform instruction, no
+// divergent path: a few cycles); only when it is not complete does one lane settle down to poll.
+__device__ __forceinline__ bool warp_wait_ready(unsigned long long *bar, uint32_t parity, int *abort_flag, int *status, int code, int lane)
+{
+    if(__all_sync(0xffffffffu, mbar_try_wait(smem_u32(bar), parity))) return true;
+    return warp_wait(bar, parity, abort_flag, status, code, lane);
+}
+
+// A read-only load that stays where it is written (the compiler keeps it ahead of the waits that follow): for operands
+// asked for early so that their trip to L2 is over by the time they are used.
+__device__ __forceinline__ float ldg_early(const float *p)
+{
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
 
 // true in exactly one lane of a converged warp
 __device__ __forceinline__ bool elect_one()

@@ -71,7 +71,7 @@ def test_two_rank_gather_reassembles_the_global_batch(tmp_path):
 
 
 def test_reference_arm_json_line_shape():
-    """--impl reference prints the contract's keys (run on a tiny budget here)."""
+    """--impl reference prints the contract's keys (a tiny sample here)."""
     import subprocess, json
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
                        capture_output=True, text=True, timeout=600)
