@@ -501,6 +501,21 @@ def run_single_conv(args):
                       "gflop": flops / 1e9, "mbytes": byts / 1e6, "status": capi.device_status()}), flush=True)
 
 
+def run_issue_probe(args):
+    """What an MMA issuing scheme costs (dlp_tf32_issue_probe): clock cycles per k-block of twelve TF32 MMAs with every barrier
+    already complete, for 64- and 128-column MMAs.  Prints a markdown table."""
+    import torch
+    from dlprimitives_b200 import capi
+    torch.cuda.set_device(0)
+    torch.zeros(1, device="cuda")
+    names = ["one thread, no waits", "lanes 0..2 each wait on one barrier, vote", "every lane tests the same barriers (uniform)",
+             "two issuer warps, pairs of k-blocks in turn"]
+    print("| scheme | N = 64 | N = 128 |\n|---|---:|---:|")
+    for scheme, name in enumerate(names):
+        print("| %d: %s | %.0f | %.0f |" % (scheme, name, capi.tf32_issue_probe(scheme, 64), capi.tf32_issue_probe(scheme, 128)))
+    print("\nfloor: twelve MMAs of 32 (N = 64) or 64 (N = 128) cycles = 384 / 768; device status %s" % (capi.device_status(),))
+
+
 def run_config_table(args):
     """The shapes of the benchmark configurations 1-4, one row each: GPU time through the C ABI (packed weights, CUDA events,
     median of a few bursts), TFLOP/s, GB/s, the applicable roof and the fraction reached, and beside it the reference's own
@@ -611,6 +626,7 @@ def main():
                     "profiler captures on a small case only, and the line then says so in config.global_batch")
     ap.add_argument("--layers-out", default=None, help="write the per-layer table (time, FLOP, bytes, applicable roof, fraction) to this JSON file")
     ap.add_argument("--configs", action="store_true", help="print the per-shape table of benchmark configurations 1-4 (GPU, with the reference CPU time beside it)")
+    ap.add_argument("--issue-probe", action="store_true", help="print what the MMA issuing schemes cost (cycles per k-block, MMA-only kernels)")
     ap.add_argument("--conv", default=None, help="profile one convolution instead: N,Cin,H,Cout,K,stride,pad[,groups[,residual]]")
     args = ap.parse_args()
     GLOBAL_BATCH = args.batch
@@ -625,6 +641,9 @@ def main():
         return
     if args.configs:
         run_config_table(args)
+        return
+    if args.issue_probe:
+        run_issue_probe(args)
         return
     if world != args.gpus:
         raise SystemExit("--gpus %d needs %d ranks (launch with torch.distributed.run --nproc-per-node %d), got WORLD_SIZE=%d"

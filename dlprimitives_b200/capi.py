@@ -57,6 +57,7 @@ SYMBOLS = {
     "dlp_device_status": (_i, [_vp, _ip]),
     "dlp_selftest_wait_expiry": (_i, [C.POINTER(C.c_int * 4), _vp]),
     "dlp_tf32_mma_rate": (_i, [C.POINTER(C.c_double), _vp]),
+    "dlp_tf32_issue_probe": (_i, [C.c_int, C.c_int, C.POINTER(C.c_double), _vp]),
     "dlp_conv2d_output_shape": (_i, [C.POINTER(ConvDesc), _i, _i, _ip, _ip]),
     "dlp_conv2d_fwd_create": (_i, [C.POINTER(ConvDesc), C.POINTER(_vp)]),
     "dlp_conv2d_fwd_destroy": (None, [_vp]),
@@ -175,6 +176,13 @@ def tf32_mma_rate(stream=None):
     """Measured dense TF32 rate of the tensor pipe on the current device, TFLOP/s (MMA-only kernel, about 2 ms)."""
     v = C.c_double(0.0)
     check(lib().dlp_tf32_mma_rate(C.byref(v), _stream(stream)))
+    return v.value
+
+
+def tf32_issue_probe(scheme, n, stream=None):
+    """Clock cycles per k-block (twelve TF32 MMAs of N = n columns) of MMA issuing scheme 0..3 with every barrier already complete."""
+    v = C.c_double(0.0)
+    check(lib().dlp_tf32_issue_probe(int(scheme), int(n), C.byref(v), _stream(stream)))
     return v.value
 
 

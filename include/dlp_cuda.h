@@ -70,6 +70,13 @@ DLP_API dlp_status dlp_selftest_wait_expiry(int observed[4], void *stream);
  * tcgen05.mma.kind::tf32 (M 128, N 128, K 8) back to back with nothing loaded or stored, timed with events on the stream
  * (about 2 ms; synchronises).  The 3xTF32 kernels can reach a third of it.  It is what roofline fractions are put beside. */
 DLP_API dlp_status dlp_tf32_mma_rate(double *tflops, void *stream);
+/* What an MMA issuing scheme costs, in clock cycles per k-block of twelve tcgen05.mma.kind::tf32 (M 128, N n = 64 or 128, K 8;
+ * no counterpart in the reference).  MMA-only like the rate above, with every barrier the loop waits on already complete, so the
+ * time is the issuing thread's own: the tensor core's queue is short, and what the thread executes between k-blocks is time the
+ * tensor core idles.  scheme 0: one thread, no waits; 1: lanes 0..2 of the warp each wait on one barrier, then a vote; 2: every
+ * lane tests the same barriers (uniform instructions; the pointwise kernel's loop with resident weights); 3: two issuer warps taking pairs of
+ * k-blocks in turn (what the contraction and staged kernels do).  Synchronises the stream. */
+DLP_API dlp_status dlp_tf32_issue_probe(int scheme, int n, double *cycles_per_kblock, void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Convolution forward.

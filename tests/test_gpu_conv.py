@@ -485,3 +485,15 @@ def test_depthwise_1x1_scale(shape):
         y = to_dev(y0) if factor else torch.full(plan.output_shape(N), float("nan"), device=DEV)
         plan.enqueue(to_dev(x), to_dev(w), to_dev(b), y, None, factor=factor)
         assert rel_err(y.cpu().numpy(), want + factor * y0) <= 1e-6, (plan.algo(), plan.kernel(), factor)
+
+
+def test_issue_probe_orders_the_schemes():
+    """The MMA-only probe behind the pointwise kernel's issue loop: uniform barrier tests cost less than a lane per barrier,
+    two issuer warps reach the 64-column MMA's own rate, and nothing runs faster than the tensor pipe (12 x 32 or 64 cycles)."""
+    from dlprimitives_b200 import capi
+    bare, divergent, uniform, two = [capi.tf32_issue_probe(s, 64) for s in range(4)]
+    assert capi.device_status() == 0
+    assert 380 <= two < bare and uniform < divergent
+    bare128, divergent128, uniform128, two128 = [capi.tf32_issue_probe(s, 128) for s in range(4)]
+    assert capi.device_status() == 0
+    assert 760 <= min(bare128, uniform128, two128) and uniform128 < divergent128 and two128 < 900
