@@ -63,6 +63,11 @@ def test_argument_validation_needs_no_device():
         capi.Gemm(False, False, 4, 4, 4, bias_mode=7)
     with pytest.raises(capi.ValidationError):
         capi.IPForward(0, 10)
+    cycles = ctypes.c_double(0.0)
+    with pytest.raises(capi.ValidationError):
+        capi.check(capi.lib().dlp_tf32_issue_probe(4, 128, ctypes.byref(cycles), None))                # schemes are 0..3
+    with pytest.raises(capi.ValidationError):
+        capi.check(capi.lib().dlp_tf32_issue_probe(0, 96, ctypes.byref(cycles), None))                 # 64 or 128 columns
     assert capi.pooling2d_output_shape(112, 112, 3, 2, 1) == (56, 56)
     assert capi.pooling2d_output_shape(7, 7, 2, 2, 0, ceil_mode=True) == (4, 4)
     d = capi.make_conv_desc(channels_in=3, channels_out=64, kernel=7, stride=2, pad=3, height=224, width=224)
