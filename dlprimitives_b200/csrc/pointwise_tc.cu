@@ -17,7 +17,7 @@
 //       - result: the epilogue warps read the accumulator from tensor memory, add bias / activation / residual,
 //         write the finished 128 x 32 block into the same epilogue buffer and one thread stores it with a
 //         tensor-map copy, which clips the pixels beyond the image and the channels beyond the tensor.
-//   * Roles (20 warps): warp 0 A copies, warp 1 MMA issue, warp 2 residual copies, warp 3 B copies, warps 8-15 converters
+//   * Roles (20 warps): warp 0 A copies, warp 1 MMA issue, warp 2 residual copies, warp 3 B copies (then second MMA issuer when the weights are resident; warp 2 is when they stream and there is no residual), warps 8-15 converters
 //     (two groups taking k-blocks in turn), warps 4-7 and 16-19 two sets of epilogue warps that take the 32-channel groups of a tile in turn (the tile's
 //     time is its epilogue: each set has its own block barrier, its own storing thread and its own stores in flight).
 //   * Every wait is bounded (device status word + abort flag, as in the general kernel); each copy-issuing
@@ -142,6 +142,8 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = q.kblocks;
+    // a warp with nothing else to do issues MMAs too: the B warp once resident weights are in, else the residual warp of a launch without residual
+    const int second_issuer = q.resident ? WARP_B : (q.has_res ? -1 : WARP_RES);
     const long long my_items = blockIdx.x < q.num_items ? (q.num_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
     if(threadIdx.x == 0) {
@@ -150,7 +152,7 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
         for(int s = 0; s < MAX_B_STAGES; s++) mbar_init(&sh->full_b[s], 1);
         for(int a = 0; a < 2; a++) { mbar_init(&sh->acc_full[a], 1); mbar_init(&sh->acc_empty[a], 4 * (GROUPS > 1 ? 2 : 1)); }
         for(int e = 0; e < MAX_E_BUFS; e++) { mbar_init(&sh->e_full[e], 1); mbar_init(&sh->e_empty[e], 1); }
-        mbar_init(&sh->drain, 1);
+        mbar_init(&sh->drain, 2);
         sh->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -163,24 +165,7 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *(volatile uint32_t *)&sh->tmem_base;
 
-    if(warp == WARP_A) {
-        // ------------------------------------------------------------------ A copies
-        if(lane == 0) {
-            uint32_t it = 0;
-            bool live = true;
-            for(long long item = blockIdx.x; item < q.num_items && live; item += gridDim.x) {
-                const Item w = decode(item, q);
-                for(int kb = 0; kb < kblocks; kb++, it++) {
-                    const int s = it % S_STAGES;
-                    if(!mbar_wait(&sh->sa_empty[s], ((it / S_STAGES) & 1) ^ 1, abort_flag, status, ST_A_EMPTY)) { live = false; break; }
-                    mbar_arrive_expect_tx(&sh->sa_full[s], A_STAGE_BYTES);
-                    tma_load_3d(a_ring + s * A_STAGE_BYTES, &tm_x, w.pix0, kb * BK, w.b, &sh->sa_full[s]);
-                }
-            }
-            drain_own(sh->sa_full, S_STAGES, it, status);
-        }
-    }
-    else if(warp == WARP_B) {
+    if(warp == WARP_B) {
         // ------------------------------------------------------------------ B copies
         if(lane == 0) {
             if(q.resident) {
@@ -212,9 +197,28 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
             }
         }
     }
-    else if(warp == WARP_RES) {
+    __syncwarp();
+
+    if(warp == WARP_A) {
+        // ------------------------------------------------------------------ A copies
+        if(lane == 0) {
+            uint32_t it = 0;
+            bool live = true;
+            for(long long item = blockIdx.x; item < q.num_items && live; item += gridDim.x) {
+                const Item w = decode(item, q);
+                for(int kb = 0; kb < kblocks; kb++, it++) {
+                    const int s = it % S_STAGES;
+                    if(!mbar_wait(&sh->sa_empty[s], ((it / S_STAGES) & 1) ^ 1, abort_flag, status, ST_A_EMPTY)) { live = false; break; }
+                    mbar_arrive_expect_tx(&sh->sa_full[s], A_STAGE_BYTES);
+                    tma_load_3d(a_ring + s * A_STAGE_BYTES, &tm_x, w.pix0, kb * BK, w.b, &sh->sa_full[s]);
+                }
+            }
+            drain_own(sh->sa_full, S_STAGES, it, status);
+        }
+    }
+    else if(warp == WARP_RES && q.has_res) {
         // ------------------------------------------------------------------ residual copies
-        if(lane == 0 && q.has_res) {
+        if(lane == 0) {
             uint32_t j = 0;
             bool live = true;
             for(long long item = blockIdx.x; item < q.num_items && live; item += gridDim.x) {
@@ -229,50 +233,87 @@ pointwise_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_c
             drain_own(sh->e_full, E_BUFS, j, status);
         }
     }
-    else if(warp == WARP_MMA) {
-        // ------------------------------------------------------------------ MMA issuer
-        // The whole warp runs the loop (warp-uniform control flow keeps the operands in uniform registers); lanes
-        // 0..2 each wait on one barrier of the k-block, one elected lane issues its twelve MMAs and the commit.
+    else if(warp == WARP_MMA || warp == second_issuer) {
+        // ------------------------------------------------------------------ MMA issuers
+        // The issuing thread blocks in tcgen05.mma at the tensor core's pace (its queue is short), so whatever else it
+        // executes between k-blocks is time the tensor core idles, and one thread cannot issue faster than an MMA per
+        // 45 cycles (a 64-column MMA is 32 cycles of work).  So: the whole warp runs the loop with uniform control flow
+        // (operands stay in uniform registers); every lane tests the same barriers, one uniform instruction each (a lane
+        // per barrier is three divergent paths: 400 cycles per k-block even when all are complete); an iteration takes two
+        // k-blocks where it can; and a warp that has nothing else to do -- the B warp once resident weights are in, the
+        // residual warp of a launch without residual -- is a second issuer: the two take the iterations in turn, one waiting for its stages and building its operands
+        // while the other's MMAs go out (a named barrier carries the turn, tcgen05 fences around it keep the MMAs of
+        // the two threads in order).  A warp whose wait gave up keeps taking its turns without issuing.
         constexpr uint32_t idesc = instr_desc_tf32(BN);
         constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO, version 1, SWIZZLE_128B
         const uint32_t region_base = ((smem_u32(b_region) & 0x3FFFF) >> 4) | (1u << 16);
-        uint32_t it = 0;
-        bool live = true;
+        const bool two = second_issuer >= 0;
+        const int me = warp == WARP_MMA ? 0 : 1;
+        const uint32_t total = uint32_t(my_items * kblocks);
+        uint32_t it = 0, step = 0, item_i = 0;
+        int kb = 0;
+        bool dead = false;
         #pragma unroll 1
-        for(long long i = 0; i < my_items && live; i++) {
-            const uint32_t buf = uint32_t(i) & 1;
-            #pragma unroll 1
-            for(int kb = 0; kb < kblocks; kb++, it++) {
-                const uint32_t s = it % T_STAGES, phase = (it / T_STAGES) & 1;
+        while(it < total) {
+            const uint32_t s = it % T_STAGES, phase = (it / T_STAGES) & 1;
+            const uint32_t buf = item_i & 1;
+            const bool pair = (s & 1) == 0 && kb + 2 <= kblocks;
+            const int n = pair ? 2 : 1;
+            const bool closes = kb + n == kblocks;
+            if(!two || int(step & 1) == me) {
                 const uint32_t sb = q.resident ? uint32_t(kb) : s;
-                // Every lane tests the same barriers, one after the other: uniform instructions.  (A lane per barrier looks
-                // cheaper and is not: three divergent paths cost some 400 cycles per k-block even when every barrier is
-                // already complete, and the tensor core idles meanwhile -- the MMA queue is short, so the issuing thread's
-                // own bookkeeping is not hidden behind the MMAs.)
-                bool ok = warp_wait_ready(&sh->full_a[s], phase, abort_flag, status, ST_MMA_A, lane);
-                if(ok && (!q.resident || i == 0)) ok = warp_wait_ready(&sh->full_b[sb], q.resident ? 0u : phase, abort_flag, status, ST_MMA_B, lane);
-                if(ok && kb == 0) ok = warp_wait_ready(&sh->acc_empty[buf], ((uint32_t(i) >> 1) & 1) ^ 1, abort_flag, status, ST_MMA_ACC, lane);
-                if(!ok) { live = false; break; }
-                tc_fence_after();
+                if(!dead) {
+                    bool ok = warp_wait_ready(&sh->full_a[s], phase, abort_flag, status, ST_MMA_A, lane);
+                    if(ok && pair) ok = warp_wait_ready(&sh->full_a[s + 1], phase, abort_flag, status, ST_MMA_A, lane);
+                    if(!q.resident || item_i == 0) {
+                        if(ok) ok = warp_wait_ready(&sh->full_b[sb], q.resident ? 0u : phase, abort_flag, status, ST_MMA_B, lane);
+                        if(ok && pair) ok = warp_wait_ready(&sh->full_b[sb + 1], q.resident ? 0u : phase, abort_flag, status, ST_MMA_B, lane);
+                    }
+                    if(ok && kb == 0) ok = warp_wait_ready(&sh->acc_empty[buf], ((item_i >> 1) & 1) ^ 1, abort_flag, status, ST_MMA_ACC, lane);
+                    if(!ok) dead = true;
+                }
                 const uint32_t d = tmem_base + buf * BN, a = tmem_base + A_COL_BASE + s * 64;
                 const uint32_t bhi = region_base + sb * (B_STAGE_BYTES >> 4), blo = bhi + (B_TILE_BYTES >> 4);
-                uint32_t ah[4], al[4];
-                uint64_t bh[4], bl[4];
+                uint32_t ah[2][4], al[2][4];
+                uint64_t bh[2][4], bl[2][4];
                 #pragma unroll
-                for(int j = 0; j < 4; j++) {
-                    ah[j] = a + 8 * j;
-                    al[j] = a + 32 + 8 * j;
-                    bh[j] = (uint64_t(DESC_HI) << 32) | (bhi + 2 * j);
-                    bl[j] = (uint64_t(DESC_HI) << 32) | (blo + 2 * j);
+                for(int h = 0; h < 2; h++)
+                    #pragma unroll
+                    for(int j = 0; j < 4; j++) {
+                        ah[h][j] = a + h * 64 + 8 * j;
+                        al[h][j] = a + h * 64 + 32 + 8 * j;
+                        bh[h][j] = (uint64_t(DESC_HI) << 32) | (bhi + h * (B_STAGE_BYTES >> 4) + 2 * j);
+                        bl[h][j] = (uint64_t(DESC_HI) << 32) | (blo + h * (B_STAGE_BYTES >> 4) + 2 * j);
+                    }
+                // my turn: the other warp has issued the iteration before this one
+                if(two && step > 0) asm volatile("bar.sync %0, 64;" ::"r"(3 + int((step - 1) & 1)) : "memory");
+                tc_fence_after();
+                if(!dead && elect_one()) {
+                    mma_kblock(d, ah[0], al[0], bh[0], bl[0], idesc, kb != 0);
+                    if(pair) mma_kblock(d, ah[1], al[1], bh[1], bl[1], idesc, 1u);
                 }
-                if(elect_one()) {
-                    mma_kblock(d, ah, al, bh, bl, idesc, kb != 0);
+                __syncwarp();
+                if(two) {
+                    tc_fence_before();
+                    asm volatile("bar.arrive %0, 64;" ::"r"(3 + int(step & 1)) : "memory");      // the other warp's turn
+                }
+                if(!dead && elect_one()) {
                     mma_commit(smem_u32(&sh->empty[s]));
-                    if(kb == kblocks - 1) mma_commit(smem_u32(&sh->acc_full[buf]));
+                    if(pair) mma_commit(smem_u32(&sh->empty[s + 1]));
+                    if(closes) mma_commit(smem_u32(&sh->acc_full[buf]));
                 }
                 __syncwarp();
             }
+            step++;
+            it += n;
+            kb += n;
+            if(kb == kblocks) { kb = 0; item_i++; }
         }
+        // the last turn handed over is taken by nobody: meet it so that both barriers are left balanced
+        if(two && step > 0 && int(step & 1) == me) asm volatile("bar.sync %0, 64;" ::"r"(3 + int((step - 1) & 1)) : "memory");
+    }
+    else if(warp == WARP_B || warp == WARP_RES) {
+        // nothing more for this warp: the B warp's one thread has issued its copies above; no residual operand in this launch
     }
     else if(warp < WARP_CONV0 || warp >= WARP_ACC1) {
         // ------------------------------------------------------------------ epilogue
@@ -415,8 +456,11 @@ teardown:
     __syncthreads();
     if(*(volatile int *)abort_flag) {
         // a wait gave up: let the MMAs already issued retire (bounded) before tensor memory goes away
+        // (a commit covers the MMAs of the thread that executes it: one from each issuer, or two from the only one)
+        if(warp == second_issuer && elect_one()) mma_commit(smem_u32(&sh->drain));
         if(warp == WARP_MMA && elect_one()) {
             mma_commit(smem_u32(&sh->drain));
+            if(second_issuer < 0) mma_commit(smem_u32(&sh->drain));
             const long long t0 = global_ns();
             while(!mbar_try_wait(&sh->drain, 0)) {
                 __nanosleep(256);
